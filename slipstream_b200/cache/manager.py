@@ -108,7 +108,7 @@ def pool_sizes(groups: list[GroupLayout], page_sizes: list[int], tokens: int, ma
     sizes = []
     for layout, page in zip(groups, page_sizes):
         pages = max(1, -(-tokens // page))
-        window = layout.spec.window
+        window = layout.spec.span  # the most keys a query of this group sees: a window's or a chunk's size
         if window is not None:
             span = min(max_model_len, window + max(1, max_step_tokens))
             pages = min(pages, max_num_seqs * (-(-span // page) + 1))
@@ -208,10 +208,7 @@ class CacheManager:
 
     def _first_needed_block(self, group: int, length: int) -> int:
         """First block that a query at position >= ``length`` can still see."""
-        window = self.groups[group].spec.window
-        if window is None:
-            return 0
-        return max(0, length - window + 1) // self.page_sizes[group]
+        return self.groups[group].spec.first_visible(length) // self.page_sizes[group]
 
     def pages_needed(self, request_id: object, new_tokens: int) -> list[int]:
         """Pages each group must still hand out to cover ``new_tokens`` more tokens."""
@@ -224,7 +221,7 @@ class CacheManager:
     def peak_pages(self, group: int, total_tokens: int, chunk: int) -> int:
         """Most pages of ``group`` a request of ``total_tokens`` holds at any time when it is fed
         at most ``chunk`` tokens a step."""
-        window = self.groups[group].spec.window
+        window = self.groups[group].spec.span
         if window is None:
             return self.blocks_for(total_tokens, group)
         span = min(total_tokens, window + max(chunk, 1))

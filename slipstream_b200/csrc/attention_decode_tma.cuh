@@ -128,7 +128,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     const int cs = FORM == 0 ? a.cluster : n_slices, n_groups = FORM == 0 ? n_slices / cs : 1, group = FORM == 0 ? slice / cs : 0;
     const int row_q = a.q_start[r], seq_len = a.seq_lens[r];
     const int pos = seq_len - 1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = key_floor(pos, window);
     const int kt_first = lo / MMA_BN, kt_last = pos / MMA_BN;
     const int n_tiles = kt_last - kt_first + 1;
     const int per = (n_tiles + n_slices - 1) / n_slices;

@@ -135,6 +135,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
     constexpr int NT = NK / 8;
     const int lane = threadIdx.x & 31;
     float s[NT][4];
+    const int floor_lo = MASK ? key_floor(pos_lo, window) : 0, floor_hi = MASK ? key_floor(pos_hi, window) : 0;
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
@@ -159,7 +160,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
             if (MASK) {  // tiles that every row of the warp sees whole skip this
                 const int key = key0_abs + key_off + n * 8 + ((lane & 3) << 1) + (e & 1);
                 const int pos = (e < 2) ? pos_lo : pos_hi;  // < 0: the row does not exist
-                ok = key <= pos && (window <= 0 || key > pos - window);
+                ok = key <= pos && key >= ((e < 2) ? floor_lo : floor_hi);
             }
             const float v = ok ? s[n][e] * scale_log2 : -INFINITY;
             s[n][e] = v;
@@ -246,7 +247,7 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
     if (rows_here <= 0) return;  // a padding tile of a captured step (uniform over the block)
     const int first_pos = seq_len - q_len + row0 / G;
     const int last_pos = seq_len - q_len + (row0 + rows_here - 1) / G;
-    const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int lo = key_floor(first_pos, window);
     __shared__ int32_t table_s[MMA_TABLE_MAX];
     const TableRef table = stage_table(table_s, block_tables + (int64_t)r * max_blocks, lo, last_pos, page_size);
     __syncthreads();
@@ -302,7 +303,7 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
         const int warp_last_pos = seq_len - q_len + (row0 + warp_last) / G;
         const bool active = warp * 16 < rows_here && kt * MMA_BN <= warp_last_pos;
         const bool whole = warp * 16 + 15 < rows_here && kt * MMA_BN + MMA_BN - 1 <= warp_first_pos &&
-                           (window <= 0 || kt * MMA_BN > warp_last_pos - window);
+                           kt * MMA_BN >= key_floor(warp_last_pos, window);
         if (active) {
             if (whole) warp_tile<D, MMA_BN, false>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
             else warp_tile<D, MMA_BN, true>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
@@ -353,7 +354,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
     const int slice = blockIdx.z;
     const int row_q = q_start[r], seq_len = seq_lens[r];
     const int pos = seq_len - 1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = key_floor(pos, window);
 
     const int kt_first = lo / MMA_BN, kt_last = pos / MMA_BN;
     const int n_tiles = kt_last - kt_first + 1;
@@ -493,7 +494,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             }
             if (kt * MMA_BN + warp * 16 <= pos) {
                 const bool whole = heads_here == 16 && kt * MMA_BN + warp * 16 + 15 <= pos &&
-                                   (window <= 0 || kt * MMA_BN + warp * 16 > pos - window);
+                                   kt * MMA_BN + warp * 16 >= key_floor(pos, window);
                 if (whole) warp_tile<D, 16, false>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
                 else warp_tile<D, 16, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
             }

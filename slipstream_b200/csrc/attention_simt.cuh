@@ -54,7 +54,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
     if (rows_here <= 0) return;  // a padding tile of a captured step (uniform over the block)
     const int pos0 = seq_len - q_len + q0;
     const int p_max = pos0 + rows_here - 1;
-    const int lo_min = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int lo_min = key_floor(pos0, window);
     const int32_t* table = block_tables + (int64_t)r * max_blocks;
 
     for (int idx = tid; idx < ATT_BM * D; idx += ATT_WARPS * 32) {
@@ -63,8 +63,10 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
     }
 
     float m[ATT_RPW], l[ATT_RPW], acc[ATT_RPW][DPL];
+    int lowest[ATT_RPW];  // the first key each of this warp's rows sees
 #pragma unroll
     for (int i = 0; i < ATT_RPW; ++i) {
+        lowest[i] = key_floor(pos0 + w * ATT_RPW + i, window);
         m[i] = -INFINITY;
         l[i] = 0.f;
 #pragma unroll
@@ -123,7 +125,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
         for (int i = 0; i < ATT_RPW; ++i) {
             const int row = w * ATT_RPW + i;
             const int pos = pos0 + row;
-            const bool ok = row < rows_here && key <= pos && (window <= 0 || key > pos - window);
+            const bool ok = row < rows_here && key <= pos && key >= lowest[i];
             const float sc = ok ? s[i] * scale : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(sc));
             const float pi = (m_new == -INFINITY) ? 0.f : expf(sc - m_new);

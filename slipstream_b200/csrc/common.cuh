@@ -40,6 +40,16 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return FAST ? __fdividef(g, 1.0f + __expf(-g)) * u : g / (1.0f + expf(-g)) * u;
 }
 
+// Which keys a query sees besides the causal rule, as one integer `span` that every attention kernel takes where
+// it used to take a window: span > 0, the last `span` keys (a sliding window); span < 0, the keys of the query's
+// own chunk of -span positions, chunks counted from the request's first token; 0, every earlier key.  The lowest
+// visible key of the query at `pos`; it never falls as `pos` grows.
+__device__ __forceinline__ int key_floor(int pos, int span) {
+    if (span > 0) return max(0, pos - span + 1);
+    if (span < 0) return pos < 0 ? 0 : (pos / (-span)) * (-span);
+    return 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -40,9 +40,11 @@ template <> struct Vec4<bf16> {
 
 // ---------------------------------------------------------------- embedding
 
+// out: [tokens][copies][hidden]: the row of the table times `scale` (the product formed in float32), written
+// `copies` times (a model with several residual streams starts them all from the embedding output).
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int hidden, int vocab, int* err) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int copies, int* err) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     const int t = blockIdx.x;
@@ -52,7 +54,7 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
         id = 0;
     }
     const T* row = table + (int64_t)id * hidden;
-    float* dst = out + (int64_t)t * hidden;
+    float* dst = out + (int64_t)t * copies * hidden;
     if (hidden % 4 == 0) {
         // four elements per load, all of a thread's loads before its first store: the row comes from memory, and
         // a decode step begins with this trip (element by element a row of 3,584 took 10 us)
@@ -67,22 +69,30 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
                 const int j = j0 + u * blockDim.x * 4;
-                if (j < hidden) Vec4<float>::store(dst + j, v[u]);
+                if (j < hidden) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[u][e] = __fmul_rn(v[u][e], scale);
+                    for (int c = 0; c < copies; ++c) Vec4<float>::store(dst + (int64_t)c * hidden + j, v[u]);
+                }
             }
         }
         return;
     }
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) dst[j] = to_float(row[j]);
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float v = __fmul_rn(to_float(row[j]), scale);
+        for (int c = 0; c < copies; ++c) dst[(int64_t)c * hidden + j] = v;
+    }
 }
 
 extern "C" int ss_embedding(const int32_t* ids, const void* table, float* out, int n_tokens,
-                            int hidden, int vocab, int dtype, int* err, cudaStream_t stream) {
+                            int hidden, int vocab, int dtype, float scale, int copies, int* err, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (copies < 1) return (int)cudaErrorInvalidValue;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == SS_BF16)
-        ss_launch(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, err);
+        ss_launch(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, copies, err);
     else
-        ss_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, err);
+        ss_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, scale, copies, err);
     return SS_LAUNCH_CHECK();
 }
 

@@ -1,0 +1,344 @@
+// Row-wise kernels for decoders that keep several residual streams and shape queries and keys after their
+// rotation: the hyper-connection step (write a branch's output into the streams, read the next branch's input out
+// of them, RMS norm) in one launch, rotation of neighbouring or half-split pairs with scaled sines, a unit RMS norm
+// per head and the key/value page write in one launch, a gated linear unit with a steeper sigmoid and clamped
+// inputs, and an element-wise sigmoid gate.  All sizes and constants are run-time parameters.  Everything the
+// formulas below name is float32; inputs and outputs are float32 or bfloat16.
+
+#include "common.cuh"
+
+// ---------------------------------------------------------------- hyper-connections
+//
+// A token has S streams x_0 .. x_{S-1} of `hidden` floats (streams: [tokens][S][hidden]).  One launch does, per token,
+//   write:  x_t <- sum_s mix[s][t] x_s + w_out[t] * y          (all t from the old streams; skipped when y is null)
+//   read:   u = sum_t w_in[t] x_t
+//   norm:   out = u / sqrt(mean(u^2) + eps) * weight            (rounded once, to the output type)
+// With `rows`, output row i is token rows[i] and the streams stay as they are (the write is only applied on the way
+// to u).  S = 1 with mix = out = in = 1 is the ordinary residual add in front of a norm.  A block per output row; a
+// row is walked twice (the second walk re-reads what the first wrote, or repeats its arithmetic), so the additions
+// behind one value never depend on the batch.
+#define HC_MAX_STREAMS 8
+
+template <typename T, int SMAX>
+__global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, const float* __restrict__ mix,
+                               const float* __restrict__ w_out, const float* __restrict__ w_in,
+                               const void* __restrict__ weight, int w_f32, T* __restrict__ out,
+                               const int32_t* __restrict__ rows, int S, int hidden, float eps) {
+    pdl_launch_dependents();
+    // the connection weights are constants of the model: read before the wait for the kernel in front
+    float m[SMAX][SMAX], wo[SMAX], wi[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) {
+        wo[s] = (y != nullptr && s < S) ? w_out[s] : 0.f;
+        wi[s] = s < S ? (w_in ? w_in[s] : 1.f) : 0.f;
+#pragma unroll
+        for (int t = 0; t < SMAX; ++t) m[s][t] = (y != nullptr && s < S && t < S) ? mix[s * S + t] : 0.f;
+    }
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* base = streams + src * (int64_t)S * hidden;
+    const T* yr = y ? y + src * (int64_t)hidden : nullptr;
+    const bool write_back = rows == nullptr && y != nullptr;
+
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float x[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) x[s] = s < S ? base[(int64_t)s * hidden + j] : 0.f;
+        float u = 0.f;
+        if (yr) {
+            const float yv = to_float(yr[j]);
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                if (t >= S) break;
+                float v = __fmul_rn(wo[t], yv);
+#pragma unroll
+                for (int s = 0; s < SMAX; ++s)
+                    if (s < S) v = fmaf(m[s][t], x[s], v);
+                if (write_back) base[(int64_t)t * hidden + j] = v;
+                u = fmaf(wi[t], v, u);
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t)
+                if (t < S) u = fmaf(wi[t], x[t], u);
+        }
+        ss = fmaf(u, u, ss);
+    }
+    ss = block_sum(ss, scratch);  // its barriers also order the writes above before the reads below
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    T* o = out + (int64_t)blockIdx.x * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float x[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) x[s] = s < S ? base[(int64_t)s * hidden + j] : 0.f;
+        float u = 0.f;
+        if (yr && !write_back) {
+            const float yv = to_float(yr[j]);
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                if (t >= S) break;
+                float v = __fmul_rn(wo[t], yv);
+#pragma unroll
+                for (int s = 0; s < SMAX; ++s)
+                    if (s < S) v = fmaf(m[s][t], x[s], v);
+                u = fmaf(wi[t], v, u);
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t)
+                if (t < S) u = fmaf(wi[t], x[t], u);
+        }
+        o[j] = from_float<T>(u * rstd * load_vec<T>(weight, j, w_f32));
+    }
+}
+
+template <typename T>
+static int launch_hc_norm(float* streams, const void* y, const float* mix, const float* w_out, const float* w_in,
+                          const void* weight, int w_f32, void* out, const int32_t* rows, int n_rows, int S, int hidden,
+                          float eps, cudaStream_t stream) {
+    const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+#define HC_GO(SMAX)                                                                                                   \
+    ss_launch(hc_norm_kernel<T, SMAX>, dim3(n_rows), dim3(threads), 0, stream, streams, (const T*)y, mix, w_out, w_in, \
+              weight, w_f32, (T*)out, rows, S, hidden, eps)
+    if (S == 1) HC_GO(1);
+    else if (S == 2) HC_GO(2);
+    else if (S <= 4) HC_GO(4);
+    else HC_GO(HC_MAX_STREAMS);
+#undef HC_GO
+    return SS_LAUNCH_CHECK();
+}
+
+// streams: float32 [tokens][S][hidden]; y: [tokens][hidden] or null; mix [S][S] (from, to), w_out [S], w_in [S] (null:
+// ones) float32 on the device; weight [hidden] in the output type or float32; rows: int32 [n_rows] or null.
+extern "C" int ss_hc_norm(float* streams, const void* y, const float* mix, const float* w_out, const float* w_in,
+                          const void* weight, int w_f32, void* out, const int32_t* rows, int n_rows, int S, int hidden,
+                          float eps, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (S < 1 || S > HC_MAX_STREAMS || (y != nullptr && (!mix || !w_out))) return (int)cudaErrorInvalidValue;
+    if (dtype == SS_BF16)
+        return launch_hc_norm<bf16>(streams, y, mix, w_out, w_in, weight, w_f32, out, rows, n_rows, S, hidden, eps, stream);
+    return launch_hc_norm<float>(streams, y, mix, w_out, w_in, weight, w_f32, out, rows, n_rows, S, hidden, eps, stream);
+}
+
+// ---------------------------------------------------------------- rotation, unit norm, page write
+//
+// A token's row holds n_q query heads, then (has_kv) n_kv key heads and n_kv value heads, D elements each, at
+// `row_stride` elements from the next token's.  A warp takes one head:
+//   rotation of the first rot_dim elements by angle = position * inv_freq[i]:
+//       pairs (2i, 2i+1) when `interleaved`, else (i, i + rot_dim/2);
+//       (a, b) -> (a c - b s, b c + a s) with c = mscale cos(angle), s = mscale sin(angle);
+//   then (norm_dim > 0) the head is divided by sqrt(sum(x^2) / norm_dim + eps): a unit RMS norm over the head's
+//   norm_dim real elements (elements beyond them are padding and zero);
+//   queries are written back in place, keys to their page (or in place when the token has no slot), values are
+//   copied to their page as they are.
+// kv layout: [page][2][kv head][offset in page][D].  D even, at most 256.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_norm_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* __restrict__ positions,
+                       const int32_t* __restrict__ slots, const float* __restrict__ inv_freq, float mscale,
+                       T* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim, int interleaved, int norm_dim,
+                       float eps, int page_size, int64_t pool_slots, int write_cache, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= n_q + 2 * n_kv) return;
+    T* src = rows + (int64_t)t * row_stride + (int64_t)h * D;
+    int64_t slot = (write_cache && slots) ? (int64_t)slots[t] : -1;
+    if (slot >= pool_slots) {
+        if (lane == 0 && h == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        slot = -1;
+    }
+    const int64_t page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? (int)(slot % page_size) : 0;
+    if (h >= n_q + n_kv) {  // a value head
+        if (slot < 0) return;
+        T* dst = kv + ((((page * 2 + 1) * n_kv + (h - n_q - n_kv)) * page_size + off) * (int64_t)D);
+        for (int d = lane; d < D; d += 32) dst[d] = src[d];
+        return;
+    }
+    T* dst = (h < n_q || slot < 0) ? src : kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+    const int half = rot_dim >> 1, pairs = D >> 1;
+    const float pos = (float)positions[t];
+    constexpr int PPL = 4;  // pairs per lane: D <= 256
+    float a[PPL], b[PPL];
+    int ia[PPL], ib[PPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < PPL; ++c) {
+        const int p = lane + 32 * c;
+        if (p >= pairs) break;
+        if (p < half) {
+            ia[c] = interleaved ? 2 * p : p;
+            ib[c] = interleaved ? 2 * p + 1 : p + half;
+        } else {  // beyond the rotated part: neighbours, unchanged
+            ia[c] = rot_dim + 2 * (p - half);
+            ib[c] = ia[c] + 1;
+        }
+        float x1 = to_float(src[ia[c]]), x2 = to_float(src[ib[c]]);
+        if (p < half) {
+            float sn, cs;
+            sincosf(__fmul_rn(pos, inv_freq[p]), &sn, &cs);
+            sn *= mscale;
+            cs *= mscale;
+            const float r1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
+            const float r2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+            x1 = r1;
+            x2 = r2;
+        }
+        a[c] = x1;
+        b[c] = x2;
+        ss = fmaf(x1, x1, ss);
+        ss = fmaf(x2, x2, ss);
+    }
+    float scale = 1.f;
+    if (norm_dim > 0) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)norm_dim + eps);
+    }
+#pragma unroll
+    for (int c = 0; c < PPL; ++c) {
+        const int p = lane + 32 * c;
+        if (p >= pairs) break;
+        dst[ia[c]] = from_float<T>(a[c] * scale);
+        dst[ib[c]] = from_float<T>(b[c] * scale);
+    }
+}
+
+extern "C" int ss_rope_norm_cache(void* rows, int64_t row_stride, const int32_t* positions, const int32_t* slots,
+                                  const float* inv_freq, float mscale, void* kv, int n_tokens, int n_q, int n_kv,
+                                  int D, int rot_dim, int interleaved, int norm_dim, float eps, int page_size,
+                                  int64_t num_pages, int write_cache, int dtype, int* err, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D < 2 || D > 256 || D % 2 || rot_dim < 0 || rot_dim > D || rot_dim % 2 || (rot_dim > 0 && !inv_freq))
+        return (int)cudaErrorInvalidValue;
+    const int heads = n_q + 2 * n_kv, warps = 4;
+    const dim3 grid(n_tokens, (heads + warps - 1) / warps);
+    const int64_t pool = num_pages * page_size;
+    if (dtype == SS_BF16)
+        ss_launch(rope_norm_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)rows, row_stride, positions, slots,
+                  inv_freq, mscale, (bf16*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps, page_size, pool,
+                  write_cache, err);
+    else
+        ss_launch(rope_norm_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)rows, row_stride, positions,
+                  slots, inv_freq, mscale, (float*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps, page_size,
+                  pool, write_cache, err);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- gated linear unit with limits
+//
+// in: [n][2 * inter], gate and up features alternating in runs of `block` as in the SwiGLU kernel.
+//   g = min(gate, limit), u = clamp(up, -limit, limit)       (limit <= 0: no clamping)
+//   out = g * sigmoid(alpha * g) * (u + shift)
+// alpha = 1, shift = 0 and no limit is silu(gate) * up.
+__device__ __forceinline__ float glu_limited(float g, float u, float alpha, float limit, float shift) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g / (1.0f + expf(-alpha * g)) * (u + shift);
+}
+
+template <typename T>
+__global__ void glu_limited_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter, int block,
+                                   float alpha, float limit, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = n * inter;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / inter;
+        const int c = (int)(idx - r * inter);
+        const T* gp = in + r * 2 * inter + (int64_t)(c / block) * 2 * block + (c % block);
+        out[idx] = from_float<T>(glu_limited(to_float(gp[0]), to_float(gp[block]), alpha, limit, shift));
+    }
+}
+
+// bfloat16, 8 gate and the 8 matching up features per thread (block % 8 == 0, 16-byte aligned rows).
+__global__ void glu_limited_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int64_t n, int inter,
+                                          int block, float alpha, float limit, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_row = inter / 8;
+    const int64_t total = n * per_row;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / per_row;
+        const int c = (int)(idx - r * per_row) * 8;
+        const bf16* gp = in + r * 2 * inter + (int64_t)(c / block) * 2 * block + (c % block);
+        const uint4 gv = *reinterpret_cast<const uint4*>(gp);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gp + block);
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
+            const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
+            const __nv_bfloat162 o2 = __floats2bfloat162_rn(
+                glu_limited(__low2float(g2), __low2float(u2), alpha, limit, shift),
+                glu_limited(__high2float(g2), __high2float(u2), alpha, limit, shift));
+            ow[e] = *reinterpret_cast<const uint32_t*>(&o2);
+        }
+        *reinterpret_cast<uint4*>(out + r * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
+extern "C" int ss_glu_limited(const void* in, void* out, int64_t n, int inter, int block, float alpha, float limit,
+                              float shift, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (block <= 0 || inter % block != 0) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    if (dtype == SS_BF16 && inter % 8 == 0 && block % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        int64_t blocks = (n * (inter / 8) + threads - 1) / threads;
+        if (blocks > ss_sm_count() * 16) blocks = ss_sm_count() * 16;
+        ss_launch(glu_limited_bf16x8_kernel, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)in, (bf16*)out, n,
+                  inter, block, alpha, limit, shift);
+        return SS_LAUNCH_CHECK();
+    }
+    int64_t blocks = (n * inter + threads - 1) / threads;
+    if (blocks > ss_sm_count() * 32) blocks = ss_sm_count() * 32;
+    if (dtype == SS_BF16)
+        ss_launch(glu_limited_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)in, (bf16*)out, n, inter,
+                  block, alpha, limit, shift);
+    else
+        ss_launch(glu_limited_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, n,
+                  inter, block, alpha, limit, shift);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- sigmoid gate
+//
+// x[t][c] *= sigmoid(gate[t][c]) for c < width; x rows are x_stride apart, gate rows gate_stride.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int64_t x_stride, const T* __restrict__ gate, int64_t gate_stride,
+                                    int64_t n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = n * width;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / width;
+        const int c = (int)(idx - r * width);
+        const float g = to_float(gate[r * gate_stride + c]);
+        T* p = x + r * x_stride + c;
+        *p = from_float<T>(to_float(*p) / (1.0f + expf(-g)));
+    }
+}
+
+extern "C" int ss_sigmoid_gate(void* x, int64_t x_stride, const void* gate, int64_t gate_stride, int64_t n, int width,
+                               int dtype, cudaStream_t stream) {
+    if (n <= 0 || width <= 0) return 0;
+    const int threads = 256;
+    int64_t blocks = (n * width + threads - 1) / threads;
+    if (blocks > ss_sm_count() * 32) blocks = ss_sm_count() * 32;
+    if (dtype == SS_BF16)
+        ss_launch(sigmoid_gate_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (bf16*)x, x_stride, (const bf16*)gate,
+                  gate_stride, n, width);
+    else
+        ss_launch(sigmoid_gate_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (float*)x, x_stride,
+                  (const float*)gate, gate_stride, n, width);
+    return SS_LAUNCH_CHECK();
+}

@@ -11,6 +11,7 @@ builders (``slipstream_b200/models/qwen2.py``) fill it from a configuration.
 
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 
 import torch
@@ -79,6 +80,19 @@ class DecoderLM:
         self.entry_index: list[int] = []  # per order entry: index within its group's page tensor
         self.entry_state: list[list[StateSpec]] = []
         by_spec: dict[CacheSpec, int] = {}
+        # An entry that reads another entry's pages may see other keys than the writer does (a wider window, another
+        # chunk size, or everything): the pages then stay for as long as a request lives.
+        kept: dict[int, CacheSpec] = {}
+        for pos, entry in enumerate(self.order):
+            if entry.cache_of is None or not 0 <= entry.block < len(self.blocks):
+                continue
+            src = entry.cache_of
+            if not 0 <= src < pos or not 0 <= self.order[src].block < len(self.blocks):
+                continue
+            own = self.blocks[self.order[src].block].mixer.cache_spec()
+            spec = self.blocks[entry.block].mixer.cache_spec()
+            if own is not None and spec is not None and (spec.window, spec.chunk) != (own.window, own.chunk):
+                kept[src] = dataclasses.replace(own, window=None, chunk=None)
         for pos, entry in enumerate(self.order):
             if not 0 <= entry.block < len(self.blocks):
                 raise ValueError(f"order[{pos}] names block {entry.block}, which does not exist")
@@ -95,11 +109,13 @@ class DecoderLM:
                 src = entry.cache_of
                 if not 0 <= src < pos or self.order[src].cache_of is not None:
                     raise ValueError(f"order[{pos}].cache_of must name an earlier entry that writes its own pages")
-                if self.blocks[self.order[src].block].mixer.cache_spec() != spec:
+                own = self.blocks[self.order[src].block].mixer.cache_spec()
+                if (own.num_kv_heads, own.head_dim, own.page_size) != (spec.num_kv_heads, spec.head_dim, spec.page_size):
                     raise ValueError(f"order[{pos}] and order[{src}] need different pages and cannot share them")
                 self.entry_group.append(self.entry_group[src])
                 self.entry_index.append(self.entry_index[src])
                 continue
+            spec = kept.get(pos, spec)
             g = by_spec.setdefault(spec, len(self.group_layouts))
             if g == len(self.group_layouts):
                 self.group_layouts.append(GroupLayout(spec))
@@ -135,6 +151,7 @@ class DecoderLM:
         if self.position_encoding is not None:
             self.position_encoding.on_embedding(residual, ctx)
         pending = normed = None
+        observer = ctx.extras.get("layer_observer")  # a caller's tap: (place in the order, stream, pending output)
         # the last block may end in the final norm when that norm needs no selection of rows
         closing = self.final_norm if ctx.extras.get("every_row_wanted") and ctx.num_logits else None
         for pos, (entry, binding) in enumerate(zip(self.order, self.bindings)):
@@ -142,6 +159,8 @@ class DecoderLM:
             following = self.blocks[self.order[pos + 1].block].first_norm() if pos + 1 < len(self.order) else closing
             residual, pending, normed = self.blocks[entry.block].forward_chained(residual, pending, normed, following,
                                                                                  ctx, binding)
+            if observer is not None:
+                observer(pos, residual, pending if normed is None else normed)
         if ctx.num_logits == 0:
             return torch.empty((0, self.lm_head.vocab_size), dtype=torch.float32, device=residual.device)
         if normed is not None:

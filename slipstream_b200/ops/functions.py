@@ -38,7 +38,7 @@ def _code(dtype: torch.dtype) -> int:
 
 
 _OPS_SIGNATURES = {
-    "ss_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ss_gather_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "ss_prepare_decode": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
                           c_void_p],
@@ -53,6 +53,12 @@ _OPS_SIGNATURES = {
     "ss_sample": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "ss_mark_seen": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ss_hc_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                   c_int, c_float, c_int, c_void_p],
+    "ss_rope_norm_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "ss_glu_limited": [c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
+    "ss_sigmoid_gate": [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p],
 }
 
 _ATTN_SIGNATURES = {
@@ -105,7 +111,7 @@ def ops_library() -> ctypes.CDLL:
     lib = _state.get("ops")
     if lib is None:
         require_cuda()
-        lib = load_library("slipstream_ops", ["ops.cu", "sampling.cu"])
+        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "sampling.cu"])
         _declare(lib, _OPS_SIGNATURES)
         _state["ops"] = lib
     return lib  # type: ignore[return-value]
@@ -222,17 +228,22 @@ def _need(t: torch.Tensor, dtype: torch.dtype | None, what: str) -> None:
 
 # --------------------------------------------------------------------------- model ops
 
-def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Rows of ``table`` [vocab, hidden] at ``token_ids`` (int32 [N]) as float32 [N, hidden]."""
+def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None, scale: float = 1.0,
+              copies: int = 1) -> torch.Tensor:
+    """Rows of ``table`` [vocab, hidden] at ``token_ids`` (int32 [N]), times ``scale``, as float32 [N, hidden]; with
+    ``copies`` > 1 as [N, copies, hidden], every copy the same (the residual streams of a model that keeps several)."""
     _need(token_ids, torch.int32, "token_ids")
     _need(table, None, "embedding table")
     n, (vocab, hidden) = token_ids.numel(), table.shape
+    shape = (n, hidden) if copies == 1 else (n, copies, hidden)
     if out is None:
-        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+        out = torch.empty(shape, dtype=torch.float32, device=table.device)
     _need(out, torch.float32, "embedding output")
+    if out.numel() != n * copies * hidden:
+        raise KernelError("embedding output has the wrong size")
     _check(ops_library().ss_embedding(token_ids.data_ptr(), table.data_ptr(), out.data_ptr(), n, hidden,
-                                      vocab, _code(table.dtype), error_word(table.device).data_ptr(),
-                                      _stream()), "embedding")
+                                      vocab, _code(table.dtype), float(scale), int(copies),
+                                      error_word(table.device).data_ptr(), _stream()), "embedding")
     return out
 
 
@@ -289,6 +300,121 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torc
                                         out.data_ptr(), _ptr(rows), n_out, hidden, float(eps),
                                         _code(out_dtype), _stream()), "add_rmsnorm")
     return out
+
+
+def hc_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor | None, w_out: torch.Tensor | None,
+            w_in: torch.Tensor | None, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: torch.Tensor | None = None) -> torch.Tensor:
+    """One hyper-connection step on ``streams`` (float32 [N, S, H], changed in place).  Write: stream t becomes
+    ``sum_s mix[s, t] * stream s + w_out[t] * y`` (skipped when ``y`` is None).  Read: ``u = sum_t w_in[t] * stream t``
+    (``w_in`` None: the plain sum).  Norm: returns ``u / sqrt(mean(u^2) + eps) * weight`` in ``out_dtype`` [N, H],
+    all in float32 with one rounding at the end.  ``mix`` [S, S], ``w_out`` [S], ``w_in`` [S]: float32 on the device.
+    With ``rows`` (int32 [M]) only those tokens are produced and the streams are left as they are."""
+    _need(streams, torch.float32, "streams")
+    if streams.dim() != 3:
+        raise KernelError("streams must be [tokens, streams, hidden]")
+    n, s, hidden = streams.shape
+    if y is not None:
+        _need(y, out_dtype, "branch output")
+        if tuple(y.shape) != (n, hidden):
+            raise KernelError(f"branch output {tuple(y.shape)} does not match the streams {tuple(streams.shape)}")
+        _need(mix, torch.float32, "mix")
+        _need(w_out, torch.float32, "w_out")
+        if mix.numel() != s * s or w_out.numel() != s:
+            raise KernelError("mix must be [S, S] and w_out [S]")
+    if w_in is not None:
+        _need(w_in, torch.float32, "w_in")
+        if w_in.numel() != s:
+            raise KernelError("w_in must be [S]")
+    _need(weight, None, "norm weight")
+    if weight.numel() != hidden or weight.dtype not in (out_dtype, torch.float32):
+        raise KernelError("norm weight has the wrong size or dtype")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    n_out = n if rows is None else rows.numel()
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=streams.device)
+    w_f32 = int(weight.dtype == torch.float32 and out_dtype != torch.float32)
+    _check(ops_library().ss_hc_norm(streams.data_ptr(), _ptr(y), _ptr(mix) if y is not None else None,
+                                    _ptr(w_out) if y is not None else None, _ptr(w_in), weight.data_ptr(), w_f32,
+                                    out.data_ptr(), _ptr(rows), n_out, s, hidden, float(eps), _code(out_dtype),
+                                    _stream()), "hc_norm")
+    return out
+
+
+def rope_norm_cache(rows: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor | None,
+                    inv_freq: torch.Tensor | None, kv: torch.Tensor | None, n_q: int, n_kv: int, head_dim: int,
+                    rotary_dim: int, *, interleaved: bool = False, mscale: float = 1.0, norm_dim: int = 0,
+                    eps: float = 0.0, write_cache: bool = True) -> None:
+    """Rotation, unit norm and page write for one layer's projected heads.  ``rows`` [N, width]: each row starts
+    with ``n_q`` query heads, then ``n_kv`` key heads and ``n_kv`` value heads (``n_kv`` 0: queries only) of
+    ``head_dim`` elements; whatever follows them in a row is left alone.  The first ``rotary_dim`` elements of
+    queries and keys are rotated by position * ``inv_freq`` in pairs (2i, 2i+1) (``interleaved``) or
+    (i, i + rotary_dim / 2), cosines and sines times ``mscale``; with ``norm_dim`` > 0 each query and key head is
+    then divided by ``sqrt(sum(x^2) / norm_dim + eps)``.  Queries change in place; keys and values go to their
+    pages ``kv`` [pages, 2, n_kv, page_size, head_dim] at ``slots`` (-1 or ``write_cache`` False: keys in place)."""
+    _need(rows, None, "projected rows")
+    _need(positions, torch.int32, "positions")
+    n, width = rows.shape
+    if width < (n_q + 2 * n_kv) * head_dim:
+        raise KernelError("the projected rows are narrower than their heads")
+    if head_dim % 2 or head_dim > 256 or rotary_dim % 2 or rotary_dim > head_dim:
+        raise KernelError("head_dim must be even and at most 256, rotary_dim even and at most head_dim")
+    if rotary_dim:
+        _need(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("inv_freq must hold rotary_dim / 2 values")
+    write = bool(write_cache and n_kv and kv is not None and slots is not None)
+    pages = page_size = 0
+    if write:
+        _need(kv, rows.dtype, "kv pages")
+        _need(slots, torch.int32, "slots")
+        if kv.dim() != 5 or kv.shape[1] != 2 or kv.shape[2] != n_kv or kv.shape[4] != head_dim:
+            raise KernelError(f"kv pages have shape {tuple(kv.shape)}, expected [pages, 2, {n_kv}, page, {head_dim}]")
+        pages, page_size = kv.shape[0], kv.shape[3]
+    _check(ops_library().ss_rope_norm_cache(rows.data_ptr(), width, positions.data_ptr(), _ptr(slots) if write else None,
+                                            _ptr(inv_freq) if rotary_dim else None, float(mscale),
+                                            _ptr(kv) if write else None, n, n_q, n_kv, head_dim, rotary_dim,
+                                            int(interleaved), int(norm_dim), float(eps), max(page_size, 1), pages,
+                                            int(write), _code(rows.dtype), error_word(rows.device).data_ptr(),
+                                            _stream()), "rope_norm_cache")
+
+
+def glu_limited(gate_up: torch.Tensor, block: int | None = None, alpha: float = 1.0, limit: float = 0.0,
+                shift: float = 0.0) -> torch.Tensor:
+    """``g * sigmoid(alpha * g) * (u + shift)`` with ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)``
+    (``limit`` 0: unclamped) for ``gate_up`` [N, 2 * I] laid out as for `swiglu`."""
+    _need(gate_up, None, "gate_up")
+    n, two_i = gate_up.shape
+    inter = two_i // 2
+    block = inter if block is None else block
+    if block < 1 or inter % block:
+        raise KernelError(f"block {block} does not divide the {inter} features")
+    out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(ops_library().ss_glu_limited(gate_up.data_ptr(), out.data_ptr(), n, inter, block, float(alpha), float(limit),
+                                        float(shift), _code(gate_up.dtype), _stream()), "glu_limited")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """``x *= sigmoid(gate)`` element by element; both [N, width], rows of either may be strided views."""
+    if x.dtype != gate.dtype or x.shape != gate.shape or x.dim() != 2 or x.stride(1) != 1 or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate takes two [N, width] tensors of one dtype with unit inner stride")
+    if not x.is_cuda:
+        raise KernelError("sigmoid_gate takes CUDA tensors")
+    _check(ops_library().ss_sigmoid_gate(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), x.shape[0],
+                                         x.shape[1], _code(x.dtype), _stream()), "sigmoid_gate")
+
+
+def key_span(window: int | None = 0, chunk: int | None = 0) -> int:
+    """The one integer the attention kernels take for what a query sees besides the causal rule: ``window`` W > 0,
+    the last W keys; ``chunk`` C > 0, the keys of the query's own chunk of C positions (counted from the request's
+    first token), passed as -C; neither: 0, every earlier key."""
+    window, chunk = int(window or 0), int(chunk or 0)
+    if window < 0 or chunk < 0:
+        raise KernelError("window and chunk must not be negative")
+    if window and chunk:
+        raise KernelError("the attention kernels take a window or a chunk, not both")
+    return window if window else -chunk
 
 
 def rope_and_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor | None,
@@ -367,8 +493,8 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None =
 def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                          block_tables: torch.Tensor, tile_req: torch.Tensor, tile_q0: torch.Tensor,
                          q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
-                         head_dim: int, scale: float, window: int = 0) -> None:
-    """Causal grouped-query attention of the step's query rows over the pages.
+                         head_dim: int, scale: float, window: int = 0, chunk: int = 0) -> None:
+    """Causal grouped-query attention of the step's query rows over the pages (``window`` / ``chunk``: `key_span`).
 
     ``q`` points at the first query head of row 0; rows are ``q_stride`` elements apart.
     ``out`` is [N, n_q * D].  ``tile_req`` / ``tile_q0`` list tiles of 16 consecutive query tokens
@@ -382,14 +508,14 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
     _check(lib.ss_attn_simt(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
                             block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                             tile_q0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
-                            n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(window or 0),
+                            n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
                             _code(q.dtype), error_word(q.device).data_ptr(), _stream()), "paged_attention_simt")
 
 
 def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                             block_tables: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor,
                             q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                            scale: float, window: int = 0) -> None:
+                            scale: float, window: int = 0, chunk: int = 0) -> None:
     """bfloat16 tensor-core attention for prompt portions and mixed batches.  A tile is 64 consecutive
     rows of one request, a row being a (query token, head of the kv group) pair in token-major order:
     ``tile_req`` / ``tile_row0`` list (request index, first row)."""
@@ -404,7 +530,7 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     _check(lib.ss_attn_prefill_mma(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
                                    block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                                    tile_row0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
-                                   n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(window or 0),
+                                   n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
                                    error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill")
 
 
@@ -489,7 +615,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
                            rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None,
-                           stages: int = 2) -> None:
+                           stages: int = 2, chunk: int = 0) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
     through shared memory; with more, the partial results (of every cluster of 8 in the TMA-fed kernel when the
@@ -538,7 +664,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     lib = attention_library(head_dim)
     args = (q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(), block_tables.data_ptr(),
             block_tables.shape[1], n_requests, q_start.data_ptr(), seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0],
-            float(scale), int(window or 0), n_slices, _ptr(inv_freq) if rotary_dim else None, rotary_dim,
+            float(scale), key_span(window, chunk), n_slices, _ptr(inv_freq) if rotary_dim else None, rotary_dim,
             int(rope is not None), _ptr(part_o), _ptr(part_lse), _ptr(counters))
     tail = (error_word(q.device).data_ptr(), _stream())
     if tma:
@@ -598,7 +724,7 @@ def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
                     ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
-                    rope: tuple[torch.Tensor | None, int] | None = None) -> None:
+                    rope: tuple[torch.Tensor | None, int] | None = None, chunk: int = 0) -> None:
     """Attention of the step's rows over the pages, choosing the kernel for the batch.
 
     ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
@@ -614,7 +740,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     if qkv.dtype == torch.float32:
         tile_req, tile_q0 = ctx.query_tiles(16)
         paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
-                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
+                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk)
         return
     group = n_q // n_kv
     if ctx.is_decode_only:
@@ -622,14 +748,14 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         longest = static or ctx.max_seq_len
         wide = ctx.extras.get("decode_wide", False) if static else is_long_context(ctx.max_seq_len)
         wide = bool(wide) and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
-        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or longest), wide,
+        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or chunk or longest), wide,
                                sm_count(qkv.device))
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
-                               stages=DECODE_RING_STAGES)
+                               stages=DECODE_RING_STAGES, chunk=chunk)
         return
-    if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
+    if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window or chunk):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
         key = ("prefill_key_parts", 128 // group, n_kv)
         parts = ctx.extras.get(key)
@@ -641,7 +767,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         return
     tile_req, tile_row0 = ctx.query_tiles(64, group)
     paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
-                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
+                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk)
 
 
 # --------------------------------------------------------------------------- sampling
@@ -1083,6 +1209,15 @@ def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     return swiglu(linear(x, weight, bias), block=block)
 
 
+def gate_up_glu(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None, block: int,
+                alpha: float, limit: float, shift: float) -> torch.Tensor:
+    """`gate_up_swiglu` with the activation of `glu_limited` (a steeper sigmoid, clamped inputs, a shifted up
+    branch): the stacked product followed by the activation kernel."""
+    if isinstance(x, PendingNorm):
+        x = x.materialize()
+    return glu_limited(linear(x, weight, bias), block, alpha, limit, shift)
+
+
 def set_programmatic_launch(enabled: bool) -> None:
     """Turn programmatic dependent launch of this package's kernels on or off (on by default)."""
     libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if isinstance(key, str) and key.startswith("attn")]
@@ -1093,6 +1228,6 @@ def set_programmatic_launch(enabled: bool) -> None:
     _state["pdl"] = bool(enabled)
 
 
-__all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
+__all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_norm", "rope_norm_cache", "glu_limited", "gate_up_glu", "sigmoid_gate", "key_span", "rope_and_cache", "swiglu",
            "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

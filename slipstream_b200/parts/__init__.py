@@ -8,9 +8,11 @@ from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .mlp import SwiGLUFeedForward
 from .norm import RMSNorm
-from .rotary import NoPositionEncoding, RotaryEncoding
+from .rotary import NoPositionEncoding, RotaryEncoding, YarnRotaryEncoding
+from .streams import ConnectedNorm, HyperConnectionBlock, StreamWrite
 
 __all__ = ["BLOCKS", "EMBEDDINGS", "HEADS", "Embedding", "Head", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "CacheSpec",
            "FeedForward", "IntoNorm", "LayerBinding", "Mixer", "Norm", "Part", "PositionEncoding", "Registry",
            "Runtime", "StateSpec", "WeightSpec", "PagedAttention", "PreNormBlock", "LMHead",
-           "TokenEmbedding", "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding"]
+           "TokenEmbedding", "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "YarnRotaryEncoding", "ConnectedNorm",
+           "HyperConnectionBlock", "StreamWrite"]

@@ -7,6 +7,20 @@ of the step's rows over each request's pages, and the output projection
 earlier keys; an integer W over the last W.  ``page_size`` asks for cache pages of
 that many tokens for this layer (layers that ask alike share a pool).  Every size is
 a constructor parameter; the part does not know which model it is in.
+
+Options beyond that (all off by default):
+``chunk`` C: a query sees only the earlier keys of its own chunk of C positions, chunks counted from the
+request's first token.  ``value_dim``: values (and the heads' outputs) of another size than queries and keys.
+``unit_norm_eps``: after the rotation every query and key head is divided by its root mean square
+(``x / sqrt(mean(x^2) + eps)``, no weight); the pages hold the keys in that form.  ``gate``: the concatenated
+heads are multiplied by ``sigmoid(W_g x)`` before the output projection (``W_g`` reads the same input as q/k/v).
+``has_kv`` False: the layer has no key/value projections and attends over pages that another layer wrote (the
+model's order names it).  ``names``: the checkpoint's tensor names by role (q, k, v, o, g, q_bias, k_bias,
+v_bias, o_bias).
+
+Heads of a size the kernels do not take (they take multiples of 16), or values of another size than keys, are
+padded with zeros where the weights are bound: q/k/v/g rows and o columns of the padding are zero, so the
+products, the scores and the outputs are what they would be without it, and no kernel knows.
 """
 
 from __future__ import annotations
@@ -26,51 +40,100 @@ class PagedAttention(Mixer):
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: PositionEncoding, qkv_bias: bool = True, out_bias: bool = False,
-                 window: int | None = None, scale: float | None = None, page_size: int | None = None) -> None:
+                 window: int | None = None, scale: float | None = None, page_size: int | None = None, *,
+                 chunk: int | None = None, value_dim: int | None = None, unit_norm_eps: float | None = None,
+                 gate: bool = False, has_kv: bool = True, names: dict[str, str] | None = None) -> None:
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})")
-        if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
-            raise ValueError(f"the attention kernels take head sizes that are multiples of 16 up to 256, not {head_dim}")
+        value_dim = head_dim if value_dim is None else int(value_dim)
+        if head_dim % 2 or not 2 <= head_dim <= 256 or not 1 <= value_dim <= 256:
+            raise ValueError(f"head sizes are even and at most 256 (values: at most 256), not {head_dim} / {value_dim}")
         if window is not None and window < 1:
             raise ValueError("window must be >= 1")
+        if chunk is not None and chunk < 1:
+            raise ValueError("chunk must be >= 1")
+        if window is not None and chunk is not None:
+            raise ValueError("a layer has a window or a chunk, not both")
         self.name = name
         self.hidden_size = hidden_size
         self.num_heads = num_heads
         self.num_kv_heads = num_kv_heads
-        self.head_dim = head_dim
+        self.key_dim = head_dim  # what the checkpoint's q and k heads hold
+        self.value_dim = value_dim
+        # what the kernels and the pages see: one size for keys and values, a multiple of 16
+        self.head_dim = -(-max(head_dim, value_dim) // 16) * 16
         self.position_encoding = position_encoding
         self.qkv_bias = qkv_bias
         self.out_bias = out_bias
         self.window = window
+        self.chunk = chunk
+        self.unit_norm_eps = None if unit_norm_eps is None else float(unit_norm_eps)
+        self.gate = bool(gate)
+        self.has_kv = bool(has_kv)
         self.page_size = page_size  # tokens per cache page this layer wants; None: the engine's default
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        n = name
+        self.names = {"q": f"{n}.q_proj.weight", "k": f"{n}.k_proj.weight", "v": f"{n}.v_proj.weight",
+                      "o": f"{n}.o_proj.weight", "g": f"{n}.g_proj.weight", "q_bias": f"{n}.q_proj.bias",
+                      "k_bias": f"{n}.k_proj.bias", "v_bias": f"{n}.v_proj.bias", "o_bias": f"{n}.o_proj.bias"}
+        self.names.update(names or {})
+
+    @property
+    def plain(self) -> bool:
+        """The layer as the fused kernels of the plain path know it: q/k/v stacked in a row and nothing after the
+        rotation (half-split pairs, unscaled sines, no unit norm, no gate, keys and values of its own)."""
+        rotary_plain = getattr(self.position_encoding, "plain", True)
+        return (rotary_plain and self.unit_norm_eps is None and not self.gate and self.has_kv
+                and self.key_dim == self.value_dim == self.head_dim)
 
     def weight_specs(self) -> list[WeightSpec]:
-        h, d, n = self.hidden_size, self.head_dim, self.name
-        specs = [WeightSpec(f"{n}.q_proj.weight", (self.num_heads * d, h)),
-                 WeightSpec(f"{n}.k_proj.weight", (self.num_kv_heads * d, h)),
-                 WeightSpec(f"{n}.v_proj.weight", (self.num_kv_heads * d, h)),
-                 WeightSpec(f"{n}.o_proj.weight", (h, self.num_heads * d))]
+        h, d, dv, names = self.hidden_size, self.key_dim, self.value_dim, self.names
+        specs = [WeightSpec(names["q"], (self.num_heads * d, h)), WeightSpec(names["o"], (h, self.num_heads * dv))]
+        if self.has_kv:
+            specs += [WeightSpec(names["k"], (self.num_kv_heads * d, h)), WeightSpec(names["v"], (self.num_kv_heads * dv, h))]
+        if self.gate:
+            specs.append(WeightSpec(names["g"], (self.num_heads * dv, h)))
         if self.qkv_bias:
-            specs += [WeightSpec(f"{n}.q_proj.bias", (self.num_heads * d,), kind="vector"),
-                      WeightSpec(f"{n}.k_proj.bias", (self.num_kv_heads * d,), kind="vector"),
-                      WeightSpec(f"{n}.v_proj.bias", (self.num_kv_heads * d,), kind="vector")]
+            specs.append(WeightSpec(names["q_bias"], (self.num_heads * d,), kind="vector"))
+            if self.has_kv:
+                specs += [WeightSpec(names["k_bias"], (self.num_kv_heads * d,), kind="vector"),
+                          WeightSpec(names["v_bias"], (self.num_kv_heads * dv,), kind="vector")]
         if self.out_bias:
-            specs.append(WeightSpec(f"{n}.o_proj.bias", (h,), kind="vector"))
+            specs.append(WeightSpec(names["o_bias"], (h,), kind="vector"))
         return specs
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(self.num_kv_heads, self.head_dim, self.window, self.page_size)
+        return CacheSpec(self.num_kv_heads, self.head_dim, self.window, self.page_size, self.chunk)
+
+    def _pad_heads(self, t: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        """[heads * size, ...] -> [heads * head_dim, ...] with zeros behind each head's ``size`` rows."""
+        if size == self.head_dim:
+            return t
+        out = t.new_zeros((heads, self.head_dim, *t.shape[1:]))
+        out[:, :size] = t.reshape(heads, size, *t.shape[1:])
+        return out.reshape(heads * self.head_dim, *t.shape[1:])
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
-        n = self.name
-        self.qkv_weight = torch.cat([weights[f"{n}.{p}_proj.weight"] for p in "qkv"], dim=0).contiguous()
+        names, nq, nkv = self.names, self.num_heads, self.num_kv_heads
+        # one stacked product: [q | k | v | g]; k and v only if the layer has them, g only with a gate
+        roles = [("q", nq, self.key_dim)]
+        if self.has_kv:
+            roles += [("k", nkv, self.key_dim), ("v", nkv, self.value_dim)]
+        if self.gate:
+            roles.append(("g", nq, self.value_dim))
+        self.qkv_weight = torch.cat([self._pad_heads(weights[names[r]], heads, size) for r, heads, size in roles],
+                                    dim=0).contiguous()
         self.qkv_b = None
         if self.qkv_bias:
-            self.qkv_b = torch.cat([weights[f"{n}.{p}_proj.bias"] for p in "qkv"]).to(runtime.dtype).contiguous()
-        self.o_weight = weights[f"{n}.o_proj.weight"]
-        self.o_b = weights[f"{n}.o_proj.bias"].to(runtime.dtype) if self.out_bias else None
+            biases = [self._pad_heads(weights[names[f"{r}_bias"]], heads, size) if r != "g"
+                      else weights[names["q"]].new_zeros(heads * self.head_dim) for r, heads, size in roles]
+            self.qkv_b = torch.cat(biases).to(runtime.dtype).contiguous()
+        o = weights[names["o"]]
+        if self.value_dim != self.head_dim:
+            o = self._pad_heads(o.t().contiguous(), nq, self.value_dim).t().contiguous()
+        self.o_weight = o
+        self.o_b = weights[names["o_bias"]].to(runtime.dtype) if self.out_bias else None
         self.position_encoding.bind(weights, runtime)
         ops.attention_library(self.head_dim)  # compile now, not inside the first step
 
@@ -84,7 +147,7 @@ class PagedAttention(Mixer):
             return bool(bf16 and ops.is_long_context(longest))
         group = self.num_heads // self.num_kv_heads
         if not bf16 or not ops.tcgen05_attention_fits(self.head_dim, self.num_heads, self.num_kv_heads, self.page_size or 16,
-                                          self.window or 0):
+                                          self.window or self.chunk or 0):
             return None
         return int(ops.prefill_key_parts(plan.q_lens, plan.seq_lens, 128 // group, self.num_kv_heads,
                                          ops.sm_count(self.runtime.device)))
@@ -124,15 +187,28 @@ class PagedAttention(Mixer):
             self.after_projection(qkv, ctx)
         inv_freq, rotary_dim = self.position_encoding.rotary_table()
         # a decode step's attention kernel rotates and writes the newest key and value itself
-        fused = (plain_projection and layer.writes_cache
+        fused = (plain_projection and self.plain and layer.writes_cache
                  and ops.fuses_rope(qkv, ctx, self.head_dim, self.num_heads, self.num_kv_heads, layer.kv.shape[3]))
-        if not fused:
+        if not self.plain:
+            if self.has_kv != layer.writes_cache:
+                raise ValueError(f"{self.name}: a layer with keys and values of its own writes its pages, one without "
+                                 "reads another layer's")
+            encoding = self.position_encoding
+            ops.rope_norm_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
+                                self.num_kv_heads if self.has_kv else 0, self.head_dim, rotary_dim,
+                                interleaved=getattr(encoding, "interleaved", False),
+                                mscale=getattr(encoding, "mscale", 1.0),
+                                norm_dim=self.key_dim if self.unit_norm_eps is not None else 0,
+                                eps=self.unit_norm_eps or 0.0, write_cache=layer.writes_cache)
+        elif not fused:
             ops.rope_and_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
                                self.num_kv_heads, self.head_dim, rotary_dim, write_cache=layer.writes_cache)
         out = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.scale, self.window or 0,
-                            rope=(inv_freq, rotary_dim) if fused else None)
+                            rope=(inv_freq, rotary_dim) if fused else None, chunk=self.chunk or 0)
+        if self.gate:
+            ops.sigmoid_gate(out, qkv[:, qkv.shape[1] - out.shape[1]:])
         if into is not None:
             return into.close(out, self.o_weight, self.o_b)
         return ops.linear(out, self.o_weight, self.o_b)

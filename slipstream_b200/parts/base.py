@@ -48,7 +48,9 @@ class WeightSpec:
 class CacheSpec:
     """Pages of keys and values one mixer needs per token.  ``window`` None means
     every earlier key stays visible; an integer W means only the last W keys are,
-    so pages wholly before the window are given back.  ``page_size``: tokens per page this mixer's kernels
+    so pages wholly before the window are given back.  ``chunk`` C: a query sees only the keys of its own chunk
+    of C positions (chunks counted from the request's first token), so pages wholly before the chunk of the
+    request's next token are given back.  ``page_size``: tokens per page this mixer's kernels
     want; None takes the engine's default.  Mixers whose specs are equal share a cache group (one page pool, one
     block table per request); a group has its own page size and its own number of pages."""
 
@@ -56,6 +58,22 @@ class CacheSpec:
     head_dim: int
     window: int | None = None
     page_size: int | None = None
+    chunk: int | None = None
+
+    def first_visible(self, position: int) -> int:
+        """The lowest key a query at ``position`` (or any later one) can see."""
+        first = 0
+        if self.window is not None:
+            first = max(first, position - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, position // self.chunk * self.chunk)
+        return first
+
+    @property
+    def span(self) -> int | None:
+        """The most keys a query can see (None: all earlier ones)."""
+        bounds = [b for b in (self.window, self.chunk) if b is not None]
+        return min(bounds) if bounds else None
 
 
 @dataclass(frozen=True)

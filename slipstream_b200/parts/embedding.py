@@ -15,20 +15,27 @@ from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime, WeightSpec
 class TokenEmbedding(Embedding):
     cuda_graph_safe = True
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int) -> None:
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0, copies: int = 1,
+                 tensor: str | None = None) -> None:
+        """``scale``: a constant the table's rows are multiplied by (in float32).  ``copies``: how many residual
+        streams the model keeps; above 1 the result is [N, copies, hidden], every stream starting as the same
+        row.  ``tensor``: the checkpoint's name of the table (default ``<name>.weight``)."""
         self.name = name
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
+        self.scale = float(scale)
+        self.copies = int(copies)
+        self.tensor = tensor or f"{name}.weight"
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec(f"{self.name}.weight", (self.vocab_size, self.hidden_size))]
+        return [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size))]
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
-        self.weight = weights[f"{self.name}.weight"]
+        self.weight = weights[self.tensor]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embedding(token_ids, self.weight)
+        return ops.embedding(token_ids, self.weight, scale=self.scale, copies=self.copies)
 
 
 @HEADS.register("linear")
@@ -36,19 +43,20 @@ class LMHead(Head):
     cuda_graph_safe = True
     takes_pending_norm = True  # ``forward`` hands x to ``ops.linear`` as it is
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None) -> None:
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None,
+                 tensor: str | None = None) -> None:
         self.name = name
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
+        self.tensor = tensor or f"{name}.weight"
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec(f"{self.name}.weight", (self.vocab_size, self.hidden_size),
-                           alias_of=self.tied_to)]
+        return [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size), alias_of=self.tied_to)]
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
-        self.weight = weights[f"{self.name}.weight"]
+        self.weight = weights[self.tensor]
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -1,6 +1,10 @@
 """Dense SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))``
 (slipstream/models/layers/mlp.py:33-40).  The gate and up matrices are stacked at
-load so that one product feeds the activation kernel."""
+load so that one product feeds the activation kernel.
+
+The activation has three constants, so that relatives of SwiGLU are the same part: with ``g = min(gate, limit)``
+and ``u = clamp(up, -limit, limit)`` (no ``limit``: unclamped) the hidden vector is
+``g * sigmoid(alpha * g) * (u + up_shift)``; alpha = 1, no limit and up_shift = 0 is SwiGLU."""
 
 from __future__ import annotations
 
@@ -17,26 +21,44 @@ class SwiGLUFeedForward(FeedForward):
     takes_into = True
     takes_pending_norm = True
 
-    def __init__(self, name: str, hidden_size: int, intermediate_size: int, bias: bool = False) -> None:
+    def __init__(self, name: str, hidden_size: int, intermediate_size: int, bias: bool = False, *,
+                 alpha: float = 1.0, limit: float | None = None, up_shift: float = 0.0,
+                 names: dict[str, str] | None = None) -> None:
+        """``names``: the checkpoint's tensor names by role (gate, up, down, gate_bias, up_bias, down_bias)."""
         self.name = name
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.bias = bias
+        self.alpha = float(alpha)
+        self.limit = None if limit is None else float(limit)
+        self.up_shift = float(up_shift)
+        if self.limit is not None and not self.limit > 0.0:
+            raise ValueError("limit must be positive")
+        n = name
+        self.names = {"gate": f"{n}.gate_proj.weight", "up": f"{n}.up_proj.weight", "down": f"{n}.down_proj.weight",
+                      "gate_bias": f"{n}.gate_proj.bias", "up_bias": f"{n}.up_proj.bias",
+                      "down_bias": f"{n}.down_proj.bias"}
+        self.names.update(names or {})
+
+    @property
+    def is_swiglu(self) -> bool:
+        return self.alpha == 1.0 and self.limit is None and self.up_shift == 0.0
 
     def weight_specs(self) -> list[WeightSpec]:
-        h, i = self.hidden_size, self.intermediate_size
-        specs = [WeightSpec(f"{self.name}.gate_proj.weight", (i, h)),
-                 WeightSpec(f"{self.name}.up_proj.weight", (i, h)),
-                 WeightSpec(f"{self.name}.down_proj.weight", (h, i))]
+        h, i, names = self.hidden_size, self.intermediate_size, self.names
+        specs = [WeightSpec(names["gate"], (i, h)), WeightSpec(names["up"], (i, h)), WeightSpec(names["down"], (h, i))]
         if self.bias:
-            specs += [WeightSpec(f"{self.name}.gate_proj.bias", (i,), kind="vector"),
-                      WeightSpec(f"{self.name}.up_proj.bias", (i,), kind="vector"),
-                      WeightSpec(f"{self.name}.down_proj.bias", (h,), kind="vector")]
+            specs += [WeightSpec(names["gate_bias"], (i,), kind="vector"),
+                      WeightSpec(names["up_bias"], (i,), kind="vector"),
+                      WeightSpec(names["down_bias"], (h,), kind="vector")]
         return specs
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
         n = self.name
+        weights = {**weights, **{f"{n}.{role}_proj.weight": weights[self.names[role]] for role in ("gate", "up", "down")}}
+        if self.bias:
+            weights.update({f"{n}.{role}_proj.bias": weights[self.names[f"{role}_bias"]] for role in ("gate", "up", "down")})
         # gate and up rows alternate in runs of `block`, so that one 128-row tile of the stacked product holds
         # 64 gate features and the 64 matching up features (the fused epilogue needs both in one block)
         i = self.intermediate_size
@@ -58,7 +80,11 @@ class SwiGLUFeedForward(FeedForward):
         return (self.gate_up.numel() + self.down.numel()) * self.down.element_size()
 
     def forward(self, x: torch.Tensor, ctx, into: IntoNorm | None = None) -> torch.Tensor:
-        hidden = ops.gate_up_swiglu(x, self.gate_up, self.gate_up_bias, self.block)
+        if self.is_swiglu:
+            hidden = ops.gate_up_swiglu(x, self.gate_up, self.gate_up_bias, self.block)
+        else:
+            hidden = ops.gate_up_glu(x, self.gate_up, self.gate_up_bias, self.block, self.alpha, self.limit or 0.0,
+                                     self.up_shift)
         if into is not None:
             return into.close(hidden, self.down, self.down_bias)
         return ops.linear(hidden, self.down, self.down_bias)

@@ -18,19 +18,20 @@ from .base import NORMS, Norm, Runtime, WeightSpec
 class RMSNorm(Norm):
     cuda_graph_safe = True
 
-    def __init__(self, name: str, size: int, eps: float) -> None:
+    def __init__(self, name: str, size: int, eps: float, tensor: str | None = None) -> None:
+        """``tensor``: the checkpoint's name of the weight vector (default ``<name>.weight``)."""
         self.name = name
         self.size = size
         self.eps = float(eps)
+        self.tensor = tensor or f"{name}.weight"
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec(f"{self.name}.weight", (self.size,), kind="vector",
-                           init=("one_plus_normal", 0.1))]
+        return [WeightSpec(self.tensor, (self.size,), kind="vector", init=("one_plus_normal", 0.1))]
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
-        self.weight = weights[f"{self.name}.weight"]
+        self.weight = weights[self.tensor]
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and model builder.
 
-``config.json``'s ``architectures[0]`` picks the entry; a folder without that key
-falls back on ``model_type`` (the reference dispatches on ``model_type`` alone,
+``config.json``'s ``architectures[0]`` (or a single ``architecture`` string) picks
+the entry; a folder without that key falls back on ``model_type`` (the reference dispatches on ``model_type`` alone,
 slipstream/models/loader.py:50-55).  Another architecture is added with
 ``register_architecture(name, ConfigClass, builder, model_types=(...))``.
 """
@@ -43,6 +43,8 @@ def architectures() -> list[str]:
 
 def resolve_architecture(data: dict[str, Any]) -> Architecture:
     names = data.get("architectures")
+    if not names and isinstance(data.get("architecture"), str):  # some designs name themselves with one string
+        names = [data["architecture"]]
     if isinstance(names, list) and names:
         name = names[0]
         if name in _ARCHITECTURES:
@@ -70,9 +72,12 @@ def load_config(folder: str | Path) -> tuple[Architecture, ModelConfigBase]:
 
 
 def _register_builtin() -> None:
+    from slipstream_b200.config.fokedra_config import FokedraConfig
+    from slipstream_b200.models.fokedra import build_fokedra
     from slipstream_b200.models.qwen2 import build_qwen2
 
     register_architecture("Qwen2ForCausalLM", Qwen2Config, build_qwen2, model_types=("qwen2", "qwen"))
+    register_architecture("Fokedra", FokedraConfig, build_fokedra)
 
 
 _register_builtin()
