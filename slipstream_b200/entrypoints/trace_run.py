@@ -37,7 +37,7 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--out", required=True)
     parser.add_argument("--max-tokens", type=int, required=True)
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page (divides 64)")
-    parser.add_argument("--max-num-seqs", type=int, default=8)
+    parser.add_argument("--max-num-seqs", type=int, default=4, help="state slots: the most requests live at a time")
     args = parser.parse_args(argv)
     if args.max_tokens < 1:
         parser.error("--max-tokens must be >= 1")
