@@ -60,6 +60,7 @@ struct DecodeTmaArgs {
     float* part_lse;
     int* counters;
     int* err;
+    const bf16* gate;  // optional sigmoid gate on the output, laid out like `out`, rows q_stride apart
 };
 
 template <int D, int NS = DT_STAGES>
@@ -429,8 +430,14 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
         } else {
             const float inv = ll > 0.f ? 1.f / ll : 0.f;
             if (n_slices == 1) {
+                float v0 = acc0 * inv, v1 = acc1 * inv;
+                if (FORM == 0 && a.gate) {
+                    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.gate + (int64_t)row_q * a.q_stride + (head0 + row) * D + d);
+                    v0 = gated<true>(v0, __low2float(g2));
+                    v1 = gated<true>(v1, __high2float(g2));
+                }
                 *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)row_q * a.out_stride + (head0 + row) * D + d) =
-                    __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
+                    __floats2bfloat162_rn(v0, v1);
             } else {
                 float* po = a.part_o + (((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d;
                 po[0] = acc0 * inv;
@@ -464,8 +471,14 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
             if (n_groups == 1) {
+                float v0 = acc0 * inv, v1 = acc1 * inv;
+                if (FORM == 0 && a.gate) {
+                    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.gate + (int64_t)row_q * a.q_stride + (head0 + row) * D + d);
+                    v0 = gated<true>(v0, __low2float(g2));
+                    v1 = gated<true>(v1, __high2float(g2));
+                }
                 *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)row_q * a.out_stride + (head0 + row) * D + d) =
-                    __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
+                    __floats2bfloat162_rn(v0, v1);
             } else {  // several clusters share the keys of this head block: the cluster's result goes to scratch
                 float* po = a.part_o + (((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d;
                 po[0] = acc0 * inv;
@@ -515,6 +528,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
         float acc = 0.f;
 #pragma unroll 8
         for (int sl = 0; sl < n_groups; ++sl) acc += __ldcg(po + (int64_t)sl * D) * w[sl];
+        if (FORM == 0 && a.gate) acc = gated<true>(acc, to_float(a.gate[(int64_t)row_q * a.q_stride + (head0 + row) * D + d]));
         a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
     }
 }

@@ -230,7 +230,7 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
                  const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_row0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
-                 int page_size, int64_t num_pages, float scale, int window, int* err) {
+                 int page_size, int64_t num_pages, float scale, int window, int* err, const bf16* __restrict__ gate) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int KSTR = D + 8;
@@ -320,9 +320,17 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
         const int gr = row0 + row, tok = gr / G, g = gr - tok * G;
         const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
         bf16* dst = out + (int64_t)(qs + tok) * out_stride + (int64_t)(kvh * G + g) * D + ((lane & 3) << 1);
+        const bf16* gt = gate ? gate + (int64_t)(qs + tok) * q_stride + (int64_t)(kvh * G + g) * D + ((lane & 3) << 1) : nullptr;
 #pragma unroll
-        for (int d = 0; d < D / 8; ++d)
-            *reinterpret_cast<__nv_bfloat162*>(dst + d * 8) = __floats2bfloat162_rn(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
+        for (int d = 0; d < D / 8; ++d) {
+            float v0 = o[d][2 * h] * inv, v1 = o[d][2 * h + 1] * inv;
+            if (gt) {
+                const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gt + d * 8);
+                v0 = gated<true>(v0, __low2float(g2));
+                v1 = gated<true>(v1, __high2float(g2));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(dst + d * 8) = __floats2bfloat162_rn(v0, v1);
+        }
     }
 }
 
@@ -337,7 +345,8 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
                 const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
                 int page_size, int64_t num_pages, float scale, int window, int n_slices, int cluster,
                 const float* __restrict__ inv_freq, int rot_dim, int fused,
-                float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err) {
+                float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err,
+                const bf16* __restrict__ gate) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     // Until pdl_wait() below, only what no kernel of this step writes is touched: the lengths, the block
     // table, and keys and values at positions before the newest token (earlier steps wrote those).  The
@@ -556,7 +565,8 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         const float val = ll > 0.f ? acc / ll : 0.f;
         const int head = kvh * G + g0 + row;
         if (n_slices == 1) {
-            out[(int64_t)row_q * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(val);
+            out[(int64_t)row_q * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(
+                gate ? gated<true>(val, to_float(gate[(int64_t)row_q * q_stride + (int64_t)head * D + d])) : val);
         } else if (cluster) {
             Pc[row * D + d] = val;
             if (d == 0) Lc[row] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
@@ -592,6 +602,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             float acc = 0.f;
 #pragma unroll
             for (int sl = 0; sl < 8; ++sl) acc += p[sl] * (lse[sl] * inv);
+            if (gate) acc = gated<true>(acc, to_float(gate[(int64_t)row_q * q_stride + (int64_t)(kvh * G + g0 + row) * D + d]));
             out[(int64_t)row_q * out_stride + (int64_t)(kvh * G + g0 + row) * D + d] = __float2bfloat16_rn(acc);
         }
         cluster_sync_before_exit();  // nobody leaves while its shared memory is still being read
@@ -640,6 +651,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         float acc = 0.f;
 #pragma unroll 8
         for (int sl = 0; sl < n_slices; ++sl) acc += __ldcg(po + (int64_t)sl * D) * w[sl];  // slices in order
+        if (gate) acc = gated<true>(acc, to_float(gate[(int64_t)row_q * q_stride + (int64_t)head * D + d]));
         out[(int64_t)row_q * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(acc);
     }
 }

@@ -35,7 +35,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_q0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                  int n_q, int n_kv, int page_size, int64_t num_pages, float scale, int window,
-                 int* err) {
+                 int* err, const T* __restrict__ gate) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int DPL = (D + 31) / 32;
@@ -166,7 +166,11 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
 #pragma unroll
         for (int c = 0; c < DPL; ++c) {
             const int d = lane + 32 * c;
-            if (d < D) dst[d] = from_float<T>(acc[i][c] * inv);
+            if (d < D) {
+                float v = acc[i][c] * inv;
+                if (gate) v = gated<sizeof(T) == 2>(v, to_float(gate[(int64_t)(qs + q0 + row) * q_stride + (int64_t)h * D + d]));
+                dst[d] = from_float<T>(v);
+            }
         }
     }
 }
@@ -176,7 +180,7 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
                      const int32_t* block_tables, int max_blocks, const int32_t* tile_req,
                      const int32_t* tile_q0, int n_tiles, const int32_t* q_start,
                      const int32_t* seq_lens, int n_q, int n_kv, int page_size, int64_t num_pages,
-                     float scale, int window, int* err, cudaStream_t stream) {
+                     float scale, int window, const void* gate, int* err, cudaStream_t stream) {
     static_assert(ATT_RPW == 4, "the kernel packs four rows per warp into a float4");
     constexpr int smem = att_simt_smem_bytes<D>();
     static SsPerDevice opted;
@@ -184,6 +188,6 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
     dim3 grid(n_tiles, n_q);
     ss_launch(attn_simt_kernel<T, D>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv, block_tables, max_blocks, tile_req,
-        tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err);
+        tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const T*)gate);
     return SS_LAUNCH_CHECK();
 }

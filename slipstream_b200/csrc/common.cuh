@@ -50,6 +50,27 @@ __device__ __forceinline__ int key_floor(int pos, int span) {
     return 0;
 }
 
+// The gated unit with three constants, of which silu_mul is the case alpha = 1, no limit, shift = 0 (and bit for bit
+// the same then): g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: unclamped);
+// g * sigmoid(alpha * g) * (u + shift).  FAST as in silu_mul.
+template <bool FAST>
+__device__ __forceinline__ float glu_mul(float g, float u, float alpha, float limit, float shift) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    const float a = alpha * g;
+    return (FAST ? __fdividef(g, 1.0f + __expf(-a)) : g / (1.0f + expf(-a))) * (u + shift);
+}
+
+// A head's output under a sigmoid gate: v * sigmoid(g).  Attention kernels take an optional `gate` pointer, laid out
+// like their output ([token][head][D]) with rows q_stride apart (the gate is projected in the same product as the
+// queries and sits in the same row), and apply it as they write.  FAST as in silu_mul.
+template <bool FAST>
+__device__ __forceinline__ float gated(float v, float g) {
+    return FAST ? __fdividef(v, 1.0f + __expf(-g)) : v / (1.0f + expf(-g));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

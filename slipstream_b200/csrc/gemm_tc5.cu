@@ -147,6 +147,8 @@ struct GemmArgs {
     const float* in_squares;
     int in_tiles;
     float in_eps;
+    // the constants of the fused gated unit (common.cuh: glu_mul); 1, 0, 0 is SwiGLU
+    float act_alpha, act_limit, act_shift;
 };
 
 __device__ __forceinline__ float bias_at(const GemmArgs& g, int f) {
@@ -158,7 +160,7 @@ __device__ __forceinline__ void store_swiglu(const GemmArgs& g, int m, int n, fl
     if (m + 64 >= g.M || n >= g.N) return;
     gate *= scale; up *= scale;
     if (g.bias) { gate += bias_at(g, m); up += bias_at(g, m + 64); }
-    const float v = silu_mul<true>(gate, up);
+    const float v = glu_mul<true>(gate, up, g.act_alpha, g.act_limit, g.act_shift);
     const int64_t at = (int64_t)n * g.ldc + (m / TC_BM) * 64 + (m % TC_BM);
     if (g.out_f32) ((float*)g.C)[at] = v;
     else ((bf16*)g.C)[at] = __float2bfloat16_rn(v);
@@ -569,6 +571,7 @@ struct ManyArgs {
     const float* in_squares;
     int in_tiles;
     float in_eps;
+    float act_alpha, act_limit, act_shift;  // as in GemmArgs
 };
 
 __device__ __forceinline__ float bias_many(const ManyArgs& g, int f) {
@@ -827,7 +830,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                             v0 += bias_many(g, n0 + gc + 2 * e); v1 += bias_many(g, n0 + gc + 2 * e + 1);
                             u0 += bias_many(g, n0 + gc + 64 + 2 * e); u1 += bias_many(g, n0 + gc + 64 + 2 * e + 1);
                         }
-                        __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul<true>(v0, u0), silu_mul<true>(v1, u1));
+                        __nv_bfloat162 v = __floats2bfloat162_rn(glu_mul<true>(v0, u0, g.act_alpha, g.act_limit, g.act_shift),
+                                                                 glu_mul<true>(v1, u1, g.act_alpha, g.act_limit, g.act_shift));
                         packed[e] = *reinterpret_cast<uint32_t*>(&v);
                     }
                     uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + f0);
@@ -939,6 +943,7 @@ struct NormEnds {  // see GemmArgs: the output added to the float32 stream, the 
     const float* in_squares = nullptr;
     int in_tiles = 0;
     float in_eps = 0.f;
+    float act_alpha = 1.f, act_limit = 0.f, act_shift = 0.f;  // the fused gated unit's constants (SwiGLU)
 };
 
 static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
@@ -967,6 +972,7 @@ static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32
     g.residual = ends.residual; g.tile_squares = ends.tile_squares; g.scaled = (bf16*)ends.scaled;
     g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
     g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
+    g.act_alpha = ends.act_alpha; g.act_limit = ends.act_limit; g.act_shift = ends.act_shift;
     const bool deep = swapped && ((K + TC_BK - 1) / TC_BK + slices - 1) / slices >= 24;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
     if (!swapped) grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, slices);
@@ -994,6 +1000,17 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
                            int swiglu, float* partial, int* counters, int* err, cudaStream_t stream) {
     return gemm_tc5(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, bn, swapped, out_f32, slices, swiglu, partial,
                     counters, NormEnds(), err, stream);
+}
+
+// The product with the fused gated unit of other constants than SwiGLU's (common.cuh: glu_mul).
+extern "C" int ss_gemm_tc5_glu(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
+                               int64_t lda, int64_t ldb, int64_t ldc, int bn, int swapped, int out_f32, int slices,
+                               float alpha, float limit, float shift, float* partial, int* counters, int* err,
+                               cudaStream_t stream) {
+    NormEnds ends;
+    ends.act_alpha = alpha; ends.act_limit = limit; ends.act_shift = shift;
+    return gemm_tc5(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, bn, swapped, out_f32, slices, 1, partial, counters,
+                    ends, err, stream);
 }
 
 // A branch's last projection into the float32 stream: the swapped product with its K slices as a thread-block
@@ -1085,6 +1102,7 @@ static int gemm_tc5_many(const void* A, const void* B, const void* bias, int bia
     g.residual = ends.residual; g.tile_squares = ends.tile_squares; g.scaled = (bf16*)ends.scaled;
     g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
     g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
+    g.act_alpha = ends.act_alpha; g.act_limit = ends.act_limit; g.act_shift = ends.act_shift;
     const int tiles2 = n_m * ((N + bn - 1) / bn);
     const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
     if (ends.residual) return launch_pair<1>(ma, mb, g, pairs, stream);
@@ -1096,6 +1114,15 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
                                 int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
                                 int* err, cudaStream_t stream) {
     return gemm_tc5_many(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, out_f32, swiglu, tile_cols, NormEnds(), err, stream);
+}
+
+// The same product with the fused gated unit of other constants than SwiGLU's.
+extern "C" int ss_gemm_tc5_many_glu(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N,
+                                    int K, int64_t lda, int64_t ldb, int64_t ldc, float alpha, float limit, float shift,
+                                    int* err, cudaStream_t stream) {
+    NormEnds ends;
+    ends.act_alpha = alpha; ends.act_limit = limit; ends.act_shift = shift;
+    return gemm_tc5_many(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, 0, 1, 0, ends, err, stream);
 }
 
 // The same product into the float32 stream (N a multiple of 16, tile_cols given): residual [M, N] += the product

@@ -233,15 +233,8 @@ extern "C" int ss_rope_norm_cache(void* rows, int64_t row_stride, const int32_t*
 // in: [n][2 * inter], gate and up features alternating in runs of `block` as in the SwiGLU kernel.
 //   g = min(gate, limit), u = clamp(up, -limit, limit)       (limit <= 0: no clamping)
 //   out = g * sigmoid(alpha * g) * (u + shift)
-// alpha = 1, shift = 0 and no limit is silu(gate) * up.
-__device__ __forceinline__ float glu_limited(float g, float u, float alpha, float limit, float shift) {
-    if (limit > 0.f) {
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-    }
-    return g / (1.0f + expf(-alpha * g)) * (u + shift);
-}
-
+// alpha = 1, shift = 0 and no limit is silu(gate) * up.  The expression is common.cuh's glu_mul, which the matrix
+// product's fused epilogue uses too: a value does not depend on which of them ran.
 template <typename T>
 __global__ void glu_limited_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter, int block,
                                    float alpha, float limit, float shift) {
@@ -253,7 +246,7 @@ __global__ void glu_limited_kernel(const T* __restrict__ in, T* __restrict__ out
         const int64_t r = idx / inter;
         const int c = (int)(idx - r * inter);
         const T* gp = in + r * 2 * inter + (int64_t)(c / block) * 2 * block + (c % block);
-        out[idx] = from_float<T>(glu_limited(to_float(gp[0]), to_float(gp[block]), alpha, limit, shift));
+        out[idx] = from_float<T>(glu_mul<sizeof(T) == 2>(to_float(gp[0]), to_float(gp[block]), alpha, limit, shift));
     }
 }
 
@@ -278,8 +271,8 @@ __global__ void glu_limited_bf16x8_kernel(const bf16* __restrict__ in, bf16* __r
             const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
             const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
             const __nv_bfloat162 o2 = __floats2bfloat162_rn(
-                glu_limited(__low2float(g2), __low2float(u2), alpha, limit, shift),
-                glu_limited(__high2float(g2), __high2float(u2), alpha, limit, shift));
+                glu_mul<true>(__low2float(g2), __low2float(u2), alpha, limit, shift),
+                glu_mul<true>(__high2float(g2), __high2float(u2), alpha, limit, shift));
             ow[e] = *reinterpret_cast<const uint32_t*>(&o2);
         }
         *reinterpret_cast<uint4*>(out + r * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);

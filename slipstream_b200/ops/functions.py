@@ -64,19 +64,19 @@ _OPS_SIGNATURES = {
 _ATTN_SIGNATURES = {
     "ss_attn_simt": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                      c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
-                     c_int, c_int, c_void_p, c_void_p],
+                     c_int, c_int, c_void_p, c_void_p, c_void_p],
     "ss_attn_prefill_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
-                            c_int, c_void_p, c_void_p],
+                            c_int, c_void_p, c_void_p, c_void_p],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p,
                             c_void_p],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 _GEMM_SIGNATURES = {
@@ -89,6 +89,10 @@ _GEMM_SIGNATURES = {
                                 c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "ss_gemm_tc5_glu": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                        c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
+    "ss_gemm_tc5_many_glu": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                             c_float, c_float, c_float, c_void_p, c_void_p],
     "ss_gemm_tc5_to_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
@@ -490,11 +494,22 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None =
     return out
 
 
+def _gate_ptr(gate: torch.Tensor | None, q: torch.Tensor, q_stride: int) -> int | None:
+    if gate is None:
+        return None
+    if gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.stride(0) != q_stride or not gate.is_cuda:
+        raise KernelError("the gate must be a view of the projected rows: same dtype, unit inner stride, rows q_stride apart")
+    return gate.data_ptr()
+
+
 def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                          block_tables: torch.Tensor, tile_req: torch.Tensor, tile_q0: torch.Tensor,
                          q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
-                         head_dim: int, scale: float, window: int = 0, chunk: int = 0) -> None:
+                         head_dim: int, scale: float, window: int = 0, chunk: int = 0,
+                         gate: torch.Tensor | None = None) -> None:
     """Causal grouped-query attention of the step's query rows over the pages (``window`` / ``chunk``: `key_span`).
+    ``gate`` (in every attention entry point): a view of the same rows as ``q`` ([N, n_q * D], rows ``q_stride``
+    apart); the output is multiplied by its sigmoid as it is written.
 
     ``q`` points at the first query head of row 0; rows are ``q_stride`` elements apart.
     ``out`` is [N, n_q * D].  ``tile_req`` / ``tile_q0`` list tiles of 16 consecutive query tokens
@@ -509,13 +524,14 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
                             block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                             tile_q0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                             n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
-                            _code(q.dtype), error_word(q.device).data_ptr(), _stream()), "paged_attention_simt")
+                            _code(q.dtype), _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream()),
+           "paged_attention_simt")
 
 
 def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                             block_tables: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor,
                             q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                            scale: float, window: int = 0, chunk: int = 0) -> None:
+                            scale: float, window: int = 0, chunk: int = 0, gate: torch.Tensor | None = None) -> None:
     """bfloat16 tensor-core attention for prompt portions and mixed batches.  A tile is 64 consecutive
     rows of one request, a row being a (query token, head of the kv group) pair in token-major order:
     ``tile_req`` / ``tile_row0`` list (request index, first row)."""
@@ -531,7 +547,8 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
                                    block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                                    tile_row0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                                    n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
-                                   error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill")
+                                   _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream()),
+           "paged_attention_prefill")
 
 
 def tcgen05_attention_fits(head_dim: int, n_q: int, n_kv: int, page_size: int, window: int) -> bool:
@@ -615,7 +632,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
                            rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None,
-                           stages: int = 2, chunk: int = 0) -> None:
+                           stages: int = 2, chunk: int = 0, gate: torch.Tensor | None = None) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
     through shared memory; with more, the partial results (of every cluster of 8 in the TMA-fed kernel when the
@@ -666,7 +683,9 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
             block_tables.shape[1], n_requests, q_start.data_ptr(), seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0],
             float(scale), key_span(window, chunk), n_slices, _ptr(inv_freq) if rotary_dim else None, rotary_dim,
             int(rope is not None), _ptr(part_o), _ptr(part_lse), _ptr(counters))
-    tail = (error_word(q.device).data_ptr(), _stream())
+    if gate is not None and rope is not None:
+        raise KernelError("a gated layer does not rotate inside the decode kernel")
+    tail = (_gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream())
     if tma:
         _check(lib.ss_attn_decode_tma(*args, int(stages), *tail), "paged_attention_decode")
     else:
@@ -724,7 +743,8 @@ def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
                     ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
-                    rope: tuple[torch.Tensor | None, int] | None = None, chunk: int = 0) -> None:
+                    rope: tuple[torch.Tensor | None, int] | None = None, chunk: int = 0,
+                    gate: torch.Tensor | None = None) -> None:
     """Attention of the step's rows over the pages, choosing the kernel for the batch.
 
     ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
@@ -734,13 +754,16 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     the tcgen05 kernel (head size 64 or 128, no window) or the mma.sync tiled kernel.
 
     ``rope`` (only where ``fuses_rope``): queries and keys of ``qkv`` are not rotated yet and the newest keys
-    and values not yet in their pages; the decode kernel does both."""
+    and values not yet in their pages; the decode kernel does both.
+
+    ``gate``: a view of ``qkv`` [N, n_q * D]; the output is multiplied by its sigmoid, inside the attention kernel
+    except behind the tcgen05 prefill kernel, where `sigmoid_gate` follows."""
     if rope is not None and not (qkv.dtype == torch.bfloat16 and ctx.is_decode_only):
         raise KernelError("only bfloat16 decode steps rotate inside the attention kernel")
     if qkv.dtype == torch.float32:
         tile_req, tile_q0 = ctx.query_tiles(16)
         paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
-                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk)
+                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate)
         return
     group = n_q // n_kv
     if ctx.is_decode_only:
@@ -753,7 +776,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
-                               stages=DECODE_RING_STAGES, chunk=chunk)
+                               stages=DECODE_RING_STAGES, chunk=chunk, gate=gate)
         return
     if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window or chunk):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
@@ -764,10 +787,12 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                                                         sm_count(qkv.device))
         paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
                                         ctx.seq_lens, n_q, n_kv, head_dim, scale, parts)
+        if gate is not None:
+            sigmoid_gate(out, gate)
         return
     tile_req, tile_row0 = ctx.query_tiles(64, group)
     paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
-                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk)
+                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate)
 
 
 # --------------------------------------------------------------------------- sampling
@@ -912,12 +937,15 @@ def _gemm_plan(tokens: int, features: int, k: int, sms: int) -> tuple[bool, int,
 
 def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None = None,
                  out_dtype: torch.dtype | None = None, plan: tuple[bool, int, int] | None = None,
-                 swiglu: bool = False, to_stream: tuple[torch.Tensor, torch.Tensor] | None = None):
+                 swiglu: bool = False, to_stream: tuple[torch.Tensor, torch.Tensor] | None = None,
+                 glu: tuple[float, float, float] | None = None):
     """``x @ weight.T + bias`` for bfloat16 ``x`` [tokens, K] and ``weight`` [features, K] on the tcgen05 tensor
     cores (TMA-fed, accumulator in tensor memory); output bfloat16 or float32.  K must be a multiple of 8.
 
     ``swiglu`` (at most 64 tokens, features a multiple of 128): the weight's rows alternate 64 gate and 64 up
     features; the result is ``silu(gate) * up`` with features / 2 columns, formed in the product's epilogue.
+
+    ``glu`` = (alpha, limit, shift) with ``swiglu``: the fused unit is `glu_limited`'s instead of SwiGLU.
 
     ``to_stream`` = (float32 stream [tokens, features], weights of the norm behind it), where `adds_to_stream`:
     the product, rounded to bfloat16, is added to the stream in place instead of being returned, and the function
@@ -986,6 +1014,16 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
                                                _ptr(counters), error_word(x.device).data_ptr(), _stream())
         _check(rc, "gemm_tcgen05 behind a pending norm")
         return out
+    if glu is not None:
+        if not swiglu:
+            raise KernelError("the constants of a gated unit come with the fused gate/up epilogue")
+        rc = gemm_library().ss_gemm_tc5_glu(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), a.shape[0],
+                                            b.shape[0], k, k, k, out.shape[1], bn, int(swapped),
+                                            int(out_dtype == torch.float32), slices, float(glu[0]), float(glu[1]),
+                                            float(glu[2]), _ptr(partial), _ptr(counters),
+                                            error_word(x.device).data_ptr(), _stream())
+        _check(rc, "gemm_tcgen05 with a gated unit")
+        return out
     rc = gemm_library().ss_gemm_tc5(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), a.shape[0],
                                     b.shape[0], k, k, k, out.shape[1], bn, int(swapped), int(out_dtype == torch.float32),
                                     slices, int(swiglu), _ptr(partial), _ptr(counters),
@@ -996,7 +1034,8 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
 
 def gemm_tcgen05_many(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None = None,
                       out_dtype: torch.dtype | None = None, swiglu: bool = False, tile_cols: int = 0,
-                      to_stream: tuple[torch.Tensor, torch.Tensor] | None = None):
+                      to_stream: tuple[torch.Tensor, torch.Tensor] | None = None,
+                      glu: tuple[float, float, float] | None = None):
     """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
     kernel, one block per SM, the blocks in pairs (``tcgen05.mma.cta_group::2``: each block of a pair loads half
     of A and half of B) that compute tiles of 256 rows with the accumulator double-buffered in tensor memory, so
@@ -1056,6 +1095,14 @@ def gemm_tcgen05_many(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bia
                                                     int(out_dtype == torch.float32), int(swiglu), tile_cols,
                                                     error_word(x.device).data_ptr(), _stream())
         _check(rc, "gemm_tcgen05_many behind a pending norm")
+        return out
+    if glu is not None:
+        if not swiglu:
+            raise KernelError("the constants of a gated unit come with the fused gate/up epilogue")
+        rc = gemm_library().ss_gemm_tc5_many_glu(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(),
+                                                 tokens, features, k, k, k, out.shape[1], float(glu[0]), float(glu[1]),
+                                                 float(glu[2]), error_word(x.device).data_ptr(), _stream())
+        _check(rc, "gemm_tcgen05_many with a gated unit")
         return out
     rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
                                          features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
@@ -1211,10 +1258,18 @@ def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
 
 def gate_up_glu(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None, block: int,
                 alpha: float, limit: float, shift: float) -> torch.Tensor:
-    """`gate_up_swiglu` with the activation of `glu_limited` (a steeper sigmoid, clamped inputs, a shifted up
-    branch): the stacked product followed by the activation kernel."""
+    """`gate_up_swiglu` with the gated unit of `glu_limited` (a steeper sigmoid, clamped inputs, a shifted up
+    branch).  Where `gate_up_swiglu` forms SwiGLU in the product's epilogue (small bfloat16 batches, long prompt
+    portions; runs of 64) this does the same with the unit's constants; everything else is the stacked product
+    followed by the activation kernel."""
     if isinstance(x, PendingNorm):
         x = x.materialize()
+    if x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0 and x.shape[1] % 8 == 0:
+        sms = sm_count(x.device)
+        if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sms):
+            return gemm_tcgen05(x, weight, bias, swiglu=True, glu=(alpha, limit, shift))
+        if many_tokens_swiglu_fits(x.shape[0], weight.shape[0], sms):
+            return gemm_tcgen05_many(x, weight, bias, swiglu=True, glu=(alpha, limit, shift))
     return glu_limited(linear(x, weight, bias), block, alpha, limit, shift)
 
 

@@ -206,9 +206,8 @@ class PagedAttention(Mixer):
         out = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.scale, self.window or 0,
-                            rope=(inv_freq, rotary_dim) if fused else None, chunk=self.chunk or 0)
-        if self.gate:
-            ops.sigmoid_gate(out, qkv[:, qkv.shape[1] - out.shape[1]:])
+                            rope=(inv_freq, rotary_dim) if fused else None, chunk=self.chunk or 0,
+                            gate=qkv[:, qkv.shape[1] - out.shape[1]:] if self.gate else None)
         if into is not None:
             return into.close(out, self.o_weight, self.o_b)
         return ops.linear(out, self.o_weight, self.o_b)

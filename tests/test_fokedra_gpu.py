@@ -346,6 +346,23 @@ def test_limited_gated_unit_and_sigmoid_gate(dtype):
     assert torch.allclose(dev.cpu().double(), want, atol=1e-6 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens, inter, k", [(5, 256, 192), (16, 1024, 64), (2048, 9472, 128), (40, 128, 72)])
+def test_gated_unit_in_the_products_epilogue(tokens, inter, k):
+    """Few tokens (the streaming product), many tokens and features (the two-SM product) and a case that takes
+    the product followed by the activation kernel: all against the plain formula on the bfloat16 inputs."""
+    from slipstream_b200 import ops
+    g = torch.Generator().manual_seed(tokens)
+    x = (torch.randn(tokens, k, generator=g)).bfloat16()
+    gate = (torch.randn(inter, k, generator=g) * 2.0 * k ** -0.5).bfloat16()
+    up = (torch.randn(inter, k, generator=g) * 2.0 * k ** -0.5).bfloat16()
+    stacked = torch.stack([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inter, k).contiguous()
+    got = ops.gate_up_glu(x.to(DEV), stacked.to(DEV), None, 64, 1.702, 1.5, 1.0).cpu().double()
+    want = plain.dense_ff(x.double(), {"gate": gate.double(), "up": up.double(), "down": torch.eye(inter, dtype=torch.float64)},
+                          {"limit": 1.5})
+    assert got.shape == want.shape and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
+
+
 def chunked_attention_plain(q, k, v, chunk, scale):
     """q [n, H, d] at the LAST n of the m positions of k, v [m, G, d]."""
     n, H, _ = q.shape
