@@ -11,6 +11,10 @@ copy bandwidth; ``points`` holds decode at batch 1 and 64; ``kernels`` each domi
 bench shape with its own roofline fraction.  Peaks come from MEASURED_PEAKS.json
 beside this file when present.  One GPU only: for --gpus above 1 it says so and exits with 2.
 
+``--compare fokedra`` times the Fokedra decoder (hyper-connected streams, gated chunked attention with unit-norm
+heads, clamped gated feed-forward) beside the Qwen2.5 decoder at equal layer sizes: prefill and decode throughput
+at three sizes, and every kernel the design adds beside the like kernel of the Qwen2.5 path with both rooflines.
+
 ``--only decode|prefill`` runs one part and prints a short line (profiling, and measurements beside the
 headline): ``--only decode --batch 1 --prompt-len 32000 --context-len 32768`` is a decode step behind a long
 context, ``--only prefill --chunk 512 --prefix 8192 --context-len 32768`` a prompt portion behind cached tokens.
@@ -346,6 +350,225 @@ def kernel_tables(which: str) -> int:
     return 0
 
 
+# Layer sizes of the comparison (those of Qwen2.5-0.5B, -7B and -14B), with few layers: the per-layer times are what
+# is compared, and the weights of either model are still larger than L2.
+COMPARE_SIZES = {
+    "0.5b": dict(vocab=151936, width=896, heads=14, kv_heads=2, dim=64, ff=4864, layers=8),
+    "7b": dict(vocab=152064, width=3584, heads=28, kv_heads=4, dim=128, ff=18944, layers=8),
+    "14b": dict(vocab=152064, width=5120, heads=40, kv_heads=8, dim=128, ff=13824, layers=6),
+}
+
+
+def compare_configs(z: dict, chunk: int, streams: int, share_kv: bool) -> tuple[dict, dict]:
+    """config.json of the Qwen2.5 decoder and of the Fokedra decoder at the sizes ``z``."""
+    qwen = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=z["vocab"], hidden_size=z["width"],
+                num_hidden_layers=z["layers"], intermediate_size=z["ff"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=z["dim"], rms_norm_eps=1e-6, rope_theta=1000000.0,
+                tie_word_embeddings=False, max_position_embeddings=8192, torch_dtype="bfloat16")
+    layers = []
+    for i in range(z["layers"]):
+        mixer = dict(dim=z["dim"], vdim=z["dim"], heads=z["heads"], kv_heads=z["kv_heads"], scale=z["dim"] ** -0.5,
+                     mask=dict(size=chunk),
+                     rot=dict(base=1000000.0, dims=z["dim"], scaling=dict(factor=4.0, original=2048, fast=32.0, slow=1.0)))
+        if share_kv and i % 2:
+            mixer["kv_from"] = i - 1
+        layers.append(dict(type="attention", mixer=mixer, mlp=dict(kind="dense", ff=z["ff"], limit=7.0)))
+    fokedra = dict(architecture="Fokedra", vocab=z["vocab"], width=z["width"], streams=streams, norm=dict(eps=1e-6),
+                   embedding=dict(scale=1.0), layers=layers, max_position_embeddings=8192)
+    return qwen, fokedra
+
+
+def run_compare(args) -> int:
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import ops
+    from slipstream_b200.engine.context import query_tiles_host, query_tiles_longest_first_host
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+
+    pk, pk_kind = peaks()
+    rng = np.random.default_rng(0)
+    dev = torch.device("cuda:0")
+    batch, ctx_tokens, T, page = args.batch, args.prompt_len, args.chunk, 16
+    result: dict = {"compare": "fokedra", "peaks": pk_kind, "batch": batch, "context": ctx_tokens, "prefill_tokens": T,
+                    "mask_chunk": args.mask_chunk, "streams": args.streams, "share_kv": bool(args.share_kv), "sizes": {}}
+
+    def measure(config: dict) -> dict:
+        folder = tempfile.mkdtemp(prefix="bench_compare_")
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(config, f)
+        pages = (batch * (ctx_tokens + args.steps + args.warmup + 16) + 2 * T) // page + 64
+        runner = ModelRunner(folder, dtype="bfloat16", page_size=page, num_pages=pages, max_num_seqs=max(batch, 4),
+                             max_model_len=8192, load_format="random", use_cuda_graphs=not args.no_graphs)
+        vocab = runner.config.vocab_size
+        # prefill: one prompt of T tokens in one step, as the captured graph a running engine replays; median of five
+        times = []
+        for w in range(getattr(runner, "mixed_graph_after", 0) + 2 + 5):
+            toks = rng.integers(0, vocab, T).tolist()
+            torch.cuda.synchronize()
+            time.sleep(0.2)  # a step by itself, as the burst peak it is compared with
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(f"p{w}", toks, [T - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            runner.release(f"p{w}")
+            times.append(start.elapsed_time(stop))
+        prefill_ms = sorted(times[-5:])[2]
+        # decode: `batch` requests behind `ctx_tokens` cached tokens each
+        ids = [f"d{i}" for i in range(batch)]
+        per_step = max(1, 4096 // ctx_tokens)
+        for i in range(0, batch, per_step):
+            runner.step([StepEntry(r, rng.integers(0, vocab, ctx_tokens).tolist(), []) for r in ids[i:i + per_step]])
+        feeds = rng.integers(0, vocab, (args.steps + args.warmup, batch)).tolist()
+        for w in range(args.warmup):
+            runner.step([StepEntry(r, [feeds[w][j]], [0]) for j, r in enumerate(ids)])
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for s in range(args.steps):
+            runner.step([StepEntry(r, [feeds[args.warmup + s][j]], [0]) for j, r in enumerate(ids)])
+        stop.record()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(stop) / args.steps
+        launches = (ops.launch_count() - launches0) // args.steps
+        nbytes = runner.weight_bytes_per_step() + batch * (ctx_tokens + args.warmup + args.steps / 2) * runner.kv_bytes_per_token()
+        out = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(T * 1000.0 / prefill_ms, 1),
+               "decode_ms": round(decode_ms, 4), "decode_tok_s": round(batch * 1000.0 / decode_ms, 1),
+               "decode_launches": int(launches), "decode_bytes_mb": round(nbytes / 1e6, 1),
+               "decode_hbm_frac": round(nbytes / (decode_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
+        runner.check()
+        del runner
+        torch.cuda.empty_cache()
+        return out
+
+    for name in (args.sizes.split(",") if args.sizes else COMPARE_SIZES):
+        qwen, fokedra = compare_configs(COMPARE_SIZES[name], args.mask_chunk, args.streams, args.share_kv)
+        result["sizes"][name] = {"qwen2": measure(qwen), "fokedra": measure(fokedra)}
+
+    # ---- every kernel the design adds, beside the like kernel of the Qwen2.5 path, at the 7B layer sizes
+    z = COMPARE_SIZES["7b"]
+    h, n_q, n_kv, d, inter, S = z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"], args.streams
+    gen = torch.Generator(device=dev).manual_seed(1)
+    COPIES = 12  # operands of each timed launch rotate through this many copies: more than L2 holds
+
+    def rand(*shape, dtype=torch.bfloat16):
+        return (torch.randn(*shape, generator=gen, device=dev) * 0.5).to(dtype)
+
+    def sweep(run) -> float:
+        for i in range(COPIES):
+            run(i)
+        times = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(COPIES):
+                run(i)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / COPIES)
+        return sorted(times)[2]
+
+    kernels: dict = {}
+
+    def hbm(name: str, us: float, nbytes: float) -> None:
+        gbs = nbytes / (us * 1e-6) / 1e9
+        kernels[name] = {"us": round(us, 2), "gbs": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 3)}
+
+    def tensor(name: str, us: float, flops: float) -> None:
+        tf = flops / (us * 1e-6) / 1e12
+        kernels[name] = {"us": round(us, 2), "tflops": round(tf, 1), "bf16_frac": round(tf / pk["bf16_tflops"], 3)}
+
+    w_norm = rand(h)
+    mix, w_out, w_in = rand(S, S, dtype=torch.float32), rand(S, dtype=torch.float32), rand(S, dtype=torch.float32)
+    for tokens, tag in ((T, "prefill"), (batch, "decode")):
+        res = [rand(tokens, h, dtype=torch.float32) for _ in range(COPIES)]
+        streams = [rand(tokens, S, h, dtype=torch.float32) for _ in range(COPIES)]
+        ys = [rand(tokens, h) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.add_rmsnorm(res[i], ys[i], w_norm, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_add_rmsnorm (qwen2)", us, tokens * h * (4 + 4 + 2 + 2))
+        us = sweep(lambda i: ops.hc_norm(streams[i], ys[i], mix, w_out, w_in, w_norm, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_hyper_connection_norm", us, tokens * h * (8 * S + 2 + 2))
+        # rotation and page write
+        width = (n_q + 2 * n_kv) * d
+        rows = [rand(tokens, width + n_q * d) for _ in range(COPIES)]
+        plain_rows = [rand(tokens, width) for _ in range(COPIES)]
+        kvs = [torch.zeros((tokens + page - 1) // page + 1, 2, n_kv, page, d, dtype=torch.bfloat16, device=dev) for _ in range(COPIES)]
+        positions = torch.arange(tokens, dtype=torch.int32, device=dev)
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        us = sweep(lambda i: ops.rope_and_cache(plain_rows[i], positions, positions, inv_freq, kvs[i], n_q, n_kv, d, d))
+        moved = tokens * d * 2.0 * (2 * n_q + 4 * n_kv)
+        hbm(f"{tag}_rope_and_cache (qwen2)", us, moved)
+        us = sweep(lambda i: ops.rope_norm_cache(rows[i], positions, positions, inv_freq, kvs[i], n_q, n_kv, d, d,
+                                                 interleaved=True, mscale=1.1, norm_dim=d, eps=1e-6))
+        hbm(f"{tag}_rope_norm_cache", us, moved)
+    gu = [rand(T, 2 * inter) for _ in range(4)]
+    COPIES_SAVED, COPIES = COPIES, 4
+    us = sweep(lambda i: ops.swiglu(gu[i], block=64))
+    hbm("prefill_swiglu (qwen2, unfused form)", us, T * inter * 6.0)
+    us = sweep(lambda i: ops.glu_limited(gu[i], 64, 1.702, 7.0, 1.0))
+    hbm("prefill_glu_limited (unfused form)", us, T * inter * 6.0)
+    del gu
+    x_h = rand(T, h)
+    w_gu = [rand(2 * inter, h) for _ in range(4)]
+    us = sweep(lambda i: ops.gate_up_swiglu(x_h, w_gu[i], None, 64))
+    tensor("prefill_gate_up_swiglu (qwen2)", us, 4.0 * T * h * inter)
+    us = sweep(lambda i: ops.gate_up_glu(x_h, w_gu[i], None, 64, 1.702, 7.0, 1.0))
+    tensor("prefill_gate_up_glu", us, 4.0 * T * h * inter)
+    x_b = rand(batch, h)
+    us = sweep(lambda i: ops.gate_up_swiglu(x_b, w_gu[i], None, 64))
+    hbm("decode_gate_up_swiglu (qwen2)", us, 4.0 * h * inter)
+    us = sweep(lambda i: ops.gate_up_glu(x_b, w_gu[i], None, 64, 1.702, 7.0, 1.0))
+    hbm("decode_gate_up_glu", us, 4.0 * h * inter)
+    del w_gu
+    COPIES = COPIES_SAVED
+
+    # attention: the chunk as long as the context, so that both designs do the same work
+    def tables(n_req: int, tokens: int) -> torch.Tensor:
+        per = (tokens + page - 1) // page
+        return torch.arange(n_req * per, dtype=torch.int32, device=dev).view(n_req, per)
+
+    kv_pages = [rand(batch * ((ctx_tokens + page - 1) // page) + 1, 2, n_kv, page, d) for _ in range(COPIES)]
+    width = (n_q + 2 * n_kv) * d
+    qkv = rand(batch, width + n_q * d)
+    att = torch.empty(batch, n_q * d, dtype=torch.bfloat16, device=dev)
+    table = tables(batch, ctx_tokens)
+    q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+    lens = torch.full((batch,), ctx_tokens, dtype=torch.int32, device=dev)
+    slices = ops.decode_slices(batch, n_kv, n_q // n_kv, ctx_tokens, False, ops.sm_count(dev))
+    nbytes = batch * ctx_tokens * 2.0 * n_kv * d * 2 + 2.0 * batch * n_q * d * 2
+    us = sweep(lambda i: ops.paged_attention_decode(qkv, qkv.shape[1], att, kv_pages[i], table, q_start, lens, batch, n_q,
+                                                    n_kv, d, d ** -0.5, 0, slices, stages=ops.functions.DECODE_RING_STAGES))
+    hbm("decode_attention (qwen2: rotation outside here)", us, nbytes)
+    us = sweep(lambda i: ops.paged_attention_decode(qkv, qkv.shape[1], att, kv_pages[i], table, q_start, lens, batch, n_q,
+                                                    n_kv, d, d ** -0.5, 0, slices, stages=ops.functions.DECODE_RING_STAGES,
+                                                    chunk=args.mask_chunk, gate=qkv[:, width:]))
+    hbm("decode_attention chunked + gate", us, nbytes + batch * n_q * d * 2.0)
+    qkv_p = rand(T, width + n_q * d)
+    att_p = torch.empty(T, n_q * d, dtype=torch.bfloat16, device=dev)
+    table_p, q_start_p = tables(1, T), torch.tensor([0, T], dtype=torch.int32, device=dev)
+    lens_p = torch.tensor([T], dtype=torch.int32, device=dev)
+    req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_longest_first_host(
+        np.asarray([T], dtype=np.int32), np.asarray([T], dtype=np.int32), 128 // (n_q // n_kv)))
+    flops = 4.0 * n_q * d * (T * (T + 1) // 2)
+    us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req, tok0,
+                                                             q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1))
+    tensor("prefill_attention tcgen05 (qwen2)", us, flops)
+    req2, row0 = (torch.from_numpy(a).to(dev) for a in query_tiles_host(np.asarray([T * (n_q // n_kv)], dtype=np.int32), 64))
+    us = sweep(lambda i: ops.paged_attention_prefill(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req2, row0, q_start_p,
+                                                     lens_p, n_q, n_kv, d, d ** -0.5, 0))
+    tensor("prefill_attention mma.sync, no mask (qwen2 with a window takes this kernel)", us, flops)
+    us = sweep(lambda i: ops.paged_attention_prefill(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req2, row0, q_start_p,
+                                                     lens_p, n_q, n_kv, d, d ** -0.5, 0, chunk=args.mask_chunk,
+                                                     gate=qkv_p[:, width:]))
+    tensor("prefill_attention mma.sync chunked + gate", us, flops)
+    result["kernels_7b"] = kernels
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -364,6 +587,12 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="run another measured workload end to end through the scheduler instead")
+    ap.add_argument("--compare", choices=["fokedra"], default=None,
+                    help="time another decoder design beside the Qwen2.5 decoder at equal layer sizes instead")
+    ap.add_argument("--sizes", default="", help="--compare: which of 0.5b,7b,14b (default: all)")
+    ap.add_argument("--mask-chunk", type=int, default=8192, help="--compare: positions per attention chunk")
+    ap.add_argument("--streams", type=int, default=2, help="--compare: residual streams")
+    ap.add_argument("--share-kv", action="store_true", help="--compare: every second layer reads the pages of the layer before")
     ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention"], default=None,
                     help="run just this part and print a short line (for profiling); gemm / attention: tables of "
                          "single kernels at several sizes")
@@ -373,6 +602,11 @@ def main() -> int:
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.compare:
+        if args.steps == 256:
+            args.steps = 64
+        args.warmup = max(args.warmup, 3)
+        return run_compare(args)
     if args.workload:
         return run_workload(args.workload, args)
     if args.only in ("gemm", "attention"):

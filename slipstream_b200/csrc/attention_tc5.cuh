@@ -147,6 +147,7 @@ struct Args {
     int64_t num_pages;
     float scale;
     int* err;
+    int span;  // what a query sees besides the causal rule (common.cuh: key_floor); 0: every earlier key
 };
 
 template <int D>
@@ -209,10 +210,13 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // (one block when the grid has one layer): block `part` takes tiles t_lo .. t_lo + n_tiles - 1, and the
     // blocks' results are combined through their shared memory at the end.
     const int splits = gridDim.z, part = blockIdx.z;
-    const int all_tiles = last_pos / FA_BN + 1;
+    // (with a span the tiles begin at the one that holds the lowest key the tile's first token sees)
+    const int t_first = key_floor(pos0, a.span) / FA_BN;
+    const int all_tiles = last_pos / FA_BN + 1 - t_first;
     const int per_part = (all_tiles + splits - 1) / splits;
-    const int t_lo = min(part * per_part, all_tiles);
-    const int n_tiles = min(all_tiles, t_lo + per_part) - t_lo;  // may be 0
+    const int rel_lo = min(part * per_part, all_tiles);
+    const int t_lo = t_first + rel_lo;
+    const int n_tiles = min(all_tiles, rel_lo + per_part) - rel_lo;  // may be 0
     const int32_t* table = a.block_tables + (int64_t)r * a.max_blocks;
 
     if (threadIdx.x == 0) {
@@ -366,6 +370,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const bool valid = row < rows_valid;
         const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
         const int pos = pos0 + tok;
+        const int lowest = key_floor(pos, a.span);  // the first key this row sees
         const float scale_log2 = a.scale * 1.4426950408889634f;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
@@ -386,6 +391,11 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int c = 0; c < 64; ++c)
                     if (key0 + c > pos) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
             }
+            if (key0 < lowest) {  // a tile that begins before the row's span: the keys in front of it are masked
+#pragma unroll
+                for (int c = 0; c < 64; ++c)
+                    if (key0 + c < lowest) sr[c >> 5][c & 31] = 0xff800000u;
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
@@ -400,7 +410,9 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, gave_up));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const float alpha = ex2(m_ref - m_new);
+                    // a row that has seen no key and sees none in this tile keeps what it has (nothing): -inf - -inf
+                    // is not a number
+                    const float alpha = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
                     l *= alpha;
 #pragma unroll 1
                     for (int c = 0; c < D; c += 32) {

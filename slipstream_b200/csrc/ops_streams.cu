@@ -125,7 +125,7 @@ extern "C" int ss_hc_norm(float* streams, const void* y, const float* mix, const
 // ---------------------------------------------------------------- rotation, unit norm, page write
 //
 // A token's row holds n_q query heads, then (has_kv) n_kv key heads and n_kv value heads, D elements each, at
-// `row_stride` elements from the next token's.  A warp takes one head:
+// `row_stride` (even) elements from the next token's.  A warp takes one head at a time:
 //   rotation of the first rot_dim elements by angle = position * inv_freq[i]:
 //       pairs (2i, 2i+1) when `interleaved`, else (i, i + rot_dim/2);
 //       (a, b) -> (a c - b s, b c + a s) with c = mscale cos(angle), s = mscale sin(angle);
@@ -134,76 +134,103 @@ extern "C" int ss_hc_norm(float* streams, const void* y, const float* mix, const
 //   queries are written back in place, keys to their page (or in place when the token has no slot), values are
 //   copied to their page as they are.
 // kv layout: [page][2][kv head][offset in page][D].  D even, at most 256.
+// Two neighbouring elements with one load or store.
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+}
+__device__ __forceinline__ void load_pair(const bf16* p, float& a, float& b) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+    a = __low2float(v); b = __high2float(v);
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// A block per token: its sines and cosines are formed once, then each warp takes heads in turn.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 rope_norm_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* __restrict__ positions,
                        const int32_t* __restrict__ slots, const float* __restrict__ inv_freq, float mscale,
                        T* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim, int interleaved, int norm_dim,
                        float eps, int page_size, int64_t pool_slots, int write_cache, int* err) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, lane = threadIdx.x & 31;
-    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (h >= n_q + 2 * n_kv) return;
-    T* src = rows + (int64_t)t * row_stride + (int64_t)h * D;
+    __shared__ float cos_s[128], sin_s[128];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int half = rot_dim >> 1, pairs = D >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(__fmul_rn(pos, inv_freq[i]), &sn, &cs);
+        sin_s[i] = sn * mscale;
+        cos_s[i] = cs * mscale;
+    }
     int64_t slot = (write_cache && slots) ? (int64_t)slots[t] : -1;
     if (slot >= pool_slots) {
-        if (lane == 0 && h == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
         slot = -1;
     }
     const int64_t page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? (int)(slot % page_size) : 0;
-    if (h >= n_q + n_kv) {  // a value head
-        if (slot < 0) return;
-        T* dst = kv + ((((page * 2 + 1) * n_kv + (h - n_q - n_kv)) * page_size + off) * (int64_t)D);
-        for (int d = lane; d < D; d += 32) dst[d] = src[d];
-        return;
-    }
-    T* dst = (h < n_q || slot < 0) ? src : kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
-    const int half = rot_dim >> 1, pairs = D >> 1;
-    const float pos = (float)positions[t];
-    constexpr int PPL = 4;  // pairs per lane: D <= 256
-    float a[PPL], b[PPL];
-    int ia[PPL], ib[PPL];
-    float ss = 0.f;
-#pragma unroll
-    for (int c = 0; c < PPL; ++c) {
-        const int p = lane + 32 * c;
-        if (p >= pairs) break;
-        if (p < half) {
-            ia[c] = interleaved ? 2 * p : p;
-            ib[c] = interleaved ? 2 * p + 1 : p + half;
-        } else {  // beyond the rotated part: neighbours, unchanged
-            ia[c] = rot_dim + 2 * (p - half);
-            ib[c] = ia[c] + 1;
+    __syncthreads();
+    for (int h = warp; h < n_q + 2 * n_kv; h += n_warps) {
+        T* src = rows + (int64_t)t * row_stride + (int64_t)h * D;
+        if (h >= n_q + n_kv) {  // a value head: copied to its page as it is
+            if (slot < 0) continue;
+            T* dst = kv + ((((page * 2 + 1) * n_kv + (h - n_q - n_kv)) * page_size + off) * (int64_t)D);
+            if ((D * sizeof(T)) % 16 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+                for (int c = lane; c < (int)(D * sizeof(T) / 16); c += 32)
+                    reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+            } else {
+                for (int d = lane; d < D; d += 32) dst[d] = src[d];
+            }
+            continue;
         }
-        float x1 = to_float(src[ia[c]]), x2 = to_float(src[ib[c]]);
-        if (p < half) {
-            float sn, cs;
-            sincosf(__fmul_rn(pos, inv_freq[p]), &sn, &cs);
-            sn *= mscale;
-            cs *= mscale;
-            const float r1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
-            const float r2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
-            x1 = r1;
-            x2 = r2;
-        }
-        a[c] = x1;
-        b[c] = x2;
-        ss = fmaf(x1, x1, ss);
-        ss = fmaf(x2, x2, ss);
-    }
-    float scale = 1.f;
-    if (norm_dim > 0) {
-        ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)norm_dim + eps);
-    }
+        T* dst = (h < n_q || slot < 0) ? src : kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+        constexpr int PPL = 4;  // pairs per lane: D <= 256
+        float a[PPL], b[PPL];
+        float ss = 0.f;
 #pragma unroll
-    for (int c = 0; c < PPL; ++c) {
-        const int p = lane + 32 * c;
-        if (p >= pairs) break;
-        dst[ia[c]] = from_float<T>(a[c] * scale);
-        dst[ib[c]] = from_float<T>(b[c] * scale);
+        for (int c = 0; c < PPL; ++c) {
+            const int p = lane + 32 * c;
+            if (p >= pairs) break;
+            float x1, x2;
+            if (p < half && !interleaved) {  // element p with element p + rot_dim / 2
+                x1 = to_float(src[p]);
+                x2 = to_float(src[p + half]);
+            } else {  // neighbours: a rotated pair (2p, 2p + 1), or two elements beyond the rotated part
+                load_pair(src + (p < half ? 2 * p : rot_dim + 2 * (p - half)), x1, x2);
+            }
+            if (p < half) {
+                const float cs = cos_s[p], sn = sin_s[p];
+                const float r1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
+                const float r2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+                x1 = r1;
+                x2 = r2;
+            }
+            a[c] = x1;
+            b[c] = x2;
+            ss = fmaf(x1, x1, ss);
+            ss = fmaf(x2, x2, ss);
+        }
+        float scale = 1.f;
+        if (norm_dim > 0) {
+            ss = warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)norm_dim + eps);
+        }
+#pragma unroll
+        for (int c = 0; c < PPL; ++c) {
+            const int p = lane + 32 * c;
+            if (p >= pairs) break;
+            if (p < half && !interleaved) {
+                dst[p] = from_float<T>(a[c] * scale);
+                dst[p + half] = from_float<T>(b[c] * scale);
+            } else {
+                store_pair(dst + (p < half ? 2 * p : rot_dim + 2 * (p - half)), a[c] * scale, b[c] * scale);
+            }
+        }
     }
 }
 
@@ -212,19 +239,20 @@ extern "C" int ss_rope_norm_cache(void* rows, int64_t row_stride, const int32_t*
                                   int D, int rot_dim, int interleaved, int norm_dim, float eps, int page_size,
                                   int64_t num_pages, int write_cache, int dtype, int* err, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (D < 2 || D > 256 || D % 2 || rot_dim < 0 || rot_dim > D || rot_dim % 2 || (rot_dim > 0 && !inv_freq))
+    if (D < 2 || D > 256 || D % 2 || rot_dim < 0 || rot_dim > D || rot_dim % 2 || (rot_dim > 0 && !inv_freq) ||
+        row_stride % 2 || ((uintptr_t)rows & 7) || ((uintptr_t)kv & 7))
         return (int)cudaErrorInvalidValue;
-    const int heads = n_q + 2 * n_kv, warps = 4;
-    const dim3 grid(n_tokens, (heads + warps - 1) / warps);
+    const int heads = n_q + 2 * n_kv;
+    const int warps = heads >= 8 ? 8 : (heads >= 4 ? 4 : 2);
     const int64_t pool = num_pages * page_size;
     if (dtype == SS_BF16)
-        ss_launch(rope_norm_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)rows, row_stride, positions, slots,
-                  inv_freq, mscale, (bf16*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps, page_size, pool,
-                  write_cache, err);
+        ss_launch(rope_norm_cache_kernel<bf16>, dim3(n_tokens), dim3(warps * 32), 0, stream, (bf16*)rows, row_stride,
+                  positions, slots, inv_freq, mscale, (bf16*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps,
+                  page_size, pool, write_cache, err);
     else
-        ss_launch(rope_norm_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)rows, row_stride, positions,
-                  slots, inv_freq, mscale, (float*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps, page_size,
-                  pool, write_cache, err);
+        ss_launch(rope_norm_cache_kernel<float>, dim3(n_tokens), dim3(warps * 32), 0, stream, (float*)rows, row_stride,
+                  positions, slots, inv_freq, mscale, (float*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps,
+                  page_size, pool, write_cache, err);
     return SS_LAUNCH_CHECK();
 }
 

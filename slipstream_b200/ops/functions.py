@@ -69,8 +69,8 @@ _ATTN_SIGNATURES = {
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
                             c_int, c_void_p, c_void_p, c_void_p],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
-                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p,
-                            c_void_p],
+                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
+                            c_void_p, c_void_p],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
@@ -552,21 +552,24 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
 
 
 def tcgen05_attention_fits(head_dim: int, n_q: int, n_kv: int, page_size: int, window: int) -> bool:
-    """Whether the tcgen05 prefill attention kernel takes this layer: head size 64 or 128, no window, pages of
-    8, 16, 32 or 64 tokens, at most 128 query heads per kv head."""
+    """Whether the tcgen05 prefill attention kernel takes this layer: head size 64 or 128, no sliding window (a
+    chunked mask it takes: `paged_attention_prefill_tcgen05`'s ``chunk``), pages of 8, 16, 32 or 64 tokens, at most 128
+    query heads per kv head."""
     return (head_dim in (64, 128) and not window and page_size in (8, 16, 32, 64) and n_q // n_kv <= 128)
 
 
 def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                                     block_tables: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
                                     q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
-                                    head_dim: int, scale: float, key_parts: int = 1) -> None:
+                                    head_dim: int, scale: float, key_parts: int = 1, chunk: int = 0) -> None:
     """bfloat16 causal attention for prompt portions and mixed batches on the tcgen05 tensor cores (Q, K, V
     tiles by TMA, S and O in tensor memory).  A tile is ``128 // (n_q // n_kv)`` consecutive query tokens of
     one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows); blocks
     start in list order, so the list should begin with the tiles that see the most keys.
     ``key_parts`` (1, 2, 4 or 8): the keys of every query tile are shared by that many blocks, a thread-block
-    cluster whose results are combined through shared memory (see ``prefill_key_parts``)."""
+    cluster whose results are combined through shared memory (see ``prefill_key_parts``).  ``chunk`` C: a query sees
+    only the earlier keys of its own chunk of C positions; the key tiles in front of a query tile's first chunk are
+    never fetched."""
     _need(out, torch.bfloat16, "attention output")
     _need(kv, torch.bfloat16, "kv pages")
     if q.dtype != torch.bfloat16:
@@ -581,7 +584,8 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
                                    block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                                    tile_tok0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                                    n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(key_parts),
-                                   error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill_tcgen05")
+                                   key_span(0, chunk), error_word(q.device).data_ptr(), _stream()),
+           "paged_attention_prefill_tcgen05")
 
 
 def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int, n_kv: int,
@@ -778,7 +782,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
                                stages=DECODE_RING_STAGES, chunk=chunk, gate=gate)
         return
-    if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window or chunk):
+    if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
         key = ("prefill_key_parts", 128 // group, n_kv)
         parts = ctx.extras.get(key)
@@ -786,7 +790,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
             parts = ctx.extras[key] = prefill_key_parts(ctx.q_lens_host, ctx.seq_lens_host, 128 // group, n_kv,
                                                         sm_count(qkv.device))
         paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
-                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts)
+                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts, chunk)
         if gate is not None:
             sigmoid_gate(out, gate)
         return

@@ -147,7 +147,7 @@ class PagedAttention(Mixer):
             return bool(bf16 and ops.is_long_context(longest))
         group = self.num_heads // self.num_kv_heads
         if not bf16 or not ops.tcgen05_attention_fits(self.head_dim, self.num_heads, self.num_kv_heads, self.page_size or 16,
-                                          self.window or self.chunk or 0):
+                                          self.window or 0):
             return None
         return int(ops.prefill_key_parts(plan.q_lens, plan.seq_lens, 128 // group, self.num_kv_heads,
                                          ops.sm_count(self.runtime.device)))

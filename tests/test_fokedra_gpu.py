@@ -380,6 +380,7 @@ def chunked_attention_plain(q, k, v, chunk, scale):
     (48, 16, 120, (121, 240, 119, 361), (1, 1, 1, 1)),      # decode: just behind, at and in front of an edge
     (64, 16, 40, (81, 80, 79, 200), (1, 1, 1, 1)),          # the TMA-fed decode kernel with a lower bound
     (64, 8, 40, (90, 130, 41), (50, 130, 2)),               # prompt portions across edges
+    (128, 16, 100, (700, 333, 64), (300, 333, 1)), (64, 32, 64, (640,), (640,)), (64, 16, 1000, (300, 90), (300, 2)),
     (32, 4, 7, (30, 64, 15), (9, 64, 15)), (16, 16, 1, (20, 5), (20, 1)), (48, 16, 120, (500,), (260,))])
 def test_chunked_visibility_in_every_attention_kernel(d, page, chunk, lens, q_lens):
     from slipstream_b200 import ops
@@ -418,6 +419,15 @@ def test_chunked_visibility_in_every_attention_kernel(d, page, chunk, lens, q_le
         ops.paged_attention_prefill(qd, n_q * d, out, kvd, tables, torch.from_numpy(req).to(DEV), torch.from_numpy(row0).to(DEV),
                                     q_start, seq, n_q, n_kv, d, scale, chunk=chunk)
         assert torch.allclose(out.cpu().double(), want, atol=3e-2)
+        if d in (64, 128):  # the tcgen05 kernel: tiles of 128 / group tokens, alone and with the keys in two parts
+            from slipstream_b200.engine.context import query_tiles_longest_first_host
+            treq, tok0 = query_tiles_longest_first_host(np.asarray(q_lens), np.asarray(lens), 128 // (n_q // n_kv))
+            for parts in (1, 2):
+                out = torch.zeros_like(qd)
+                ops.paged_attention_prefill_tcgen05(qd, n_q * d, out, kvd, tables, torch.from_numpy(treq).to(DEV),
+                                                    torch.from_numpy(tok0).to(DEV), q_start, seq, n_q, n_kv, d, scale, parts,
+                                                    chunk=chunk)
+                assert torch.allclose(out.cpu().double(), want, atol=3e-2), parts
         if max(q_lens) == 1:
             for slices in (1, 2, 4):
                 for tma in ((False, True) if d in (64, 128) else (False,)):
