@@ -148,7 +148,8 @@ __device__ __forceinline__ void store_pair(bf16* p, float a, float b) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
-// A block per token: its sines and cosines are formed once, then each warp takes heads in turn.
+// A block per token and group of heads (grid.y), a warp per head: every head's loads are in flight at once, and the
+// token's sines and cosines are formed once per block.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_norm_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* __restrict__ positions,
@@ -175,7 +176,7 @@ rope_norm_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* 
     const int64_t page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? (int)(slot % page_size) : 0;
     __syncthreads();
-    for (int h = warp; h < n_q + 2 * n_kv; h += n_warps) {
+    for (int h = blockIdx.y * n_warps + warp; h < n_q + 2 * n_kv; h += gridDim.y * n_warps) {
         T* src = rows + (int64_t)t * row_stride + (int64_t)h * D;
         if (h >= n_q + n_kv) {  // a value head: copied to its page as it is
             if (slot < 0) continue;
@@ -234,6 +235,105 @@ rope_norm_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* 
     }
 }
 
+// bfloat16 with 16-byte accesses (neighbouring pairs, D a multiple of 8, 16-byte aligned rows): LPH lanes share a
+// head, 8 elements (4 pairs) each, so a warp holds 32 / LPH heads at a time and two such sets are in flight per
+// thread; value heads are copied 16 bytes a thread.  A block per token.
+template <int LPH>
+__global__ void __launch_bounds__(256)
+rope_norm_cache_bf16x8_kernel(bf16* __restrict__ rows, int64_t row_stride, const int32_t* __restrict__ positions,
+                              const int32_t* __restrict__ slots, const float* __restrict__ inv_freq, float mscale,
+                              bf16* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim, int norm_dim, float eps,
+                              int page_size, int64_t pool_slots, int write_cache, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float cos_s[128], sin_s[128];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int half = rot_dim >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(__fmul_rn(pos, inv_freq[i]), &sn, &cs);
+        sin_s[i] = sn * mscale;
+        cos_s[i] = cs * mscale;
+    }
+    int64_t slot = (write_cache && slots) ? (int64_t)slots[t] : -1;
+    if (slot >= pool_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        slot = -1;
+    }
+    const int64_t page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? (int)(slot % page_size) : 0;
+    bf16* row = rows + (int64_t)t * row_stride;
+    // values first: their copies are in flight while the sines are formed
+    if (slot >= 0) {
+        const int cpr = D / 8;
+        for (int idx = threadIdx.x; idx < n_kv * cpr; idx += blockDim.x) {
+            const int h = idx / cpr, c = idx - h * cpr;
+            reinterpret_cast<uint4*>(kv + (((page * 2 + 1) * n_kv + h) * page_size + off) * (int64_t)D)[c] =
+                reinterpret_cast<const uint4*>(row + (int64_t)(n_q + n_kv + h) * D)[c];
+        }
+    }
+    __syncthreads();
+    constexpr int HPW = 32 / LPH, U = 2;
+    const int sub = lane / LPH, l = lane % LPH;
+    const bool lane_on = l * 8 < D;
+    const int heads = n_q + n_kv, stride = n_warps * HPW;
+    for (int hb = warp * HPW; hb < heads; hb += stride * U) {  // the same trips for every lane of a warp (shuffles below)
+        const int h0 = hb + sub;
+        uint4 raw[U];
+        bool on[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int h = h0 + u * stride;
+            on[u] = lane_on && h < heads;
+            if (on[u]) raw[u] = *reinterpret_cast<const uint4*>(row + (int64_t)h * D + l * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int h = h0 + u * stride;
+            float x[8];
+            float ss = 0.f;
+            if (on[u]) {
+                const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+                    float x1 = __low2float(v), x2 = __high2float(v);
+                    const int p = l * 4 + e;
+                    if (p < half) {
+                        const float cs = cos_s[p], sn = sin_s[p];
+                        const float r1 = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(-x2, sn));
+                        const float r2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+                        x1 = r1;
+                        x2 = r2;
+                    }
+                    x[2 * e] = x1;
+                    x[2 * e + 1] = x2;
+                    ss = fmaf(x1, x1, ss);
+                    ss = fmaf(x2, x2, ss);
+                }
+            }
+            float scale = 1.f;
+            if (norm_dim > 0) {  // the whole warp takes part in the shuffles
+#pragma unroll
+                for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                scale = 1.0f / sqrtf(ss / (float)norm_dim + eps);
+            }
+            if (on[u]) {
+                bf16* dst = (h < n_q || slot < 0) ? row + (int64_t)h * D
+                                                  : kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+                uint32_t o4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(x[2 * e] * scale, x[2 * e + 1] * scale);
+                    o4[e] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(dst + l * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+        }
+    }
+}
+
 extern "C" int ss_rope_norm_cache(void* rows, int64_t row_stride, const int32_t* positions, const int32_t* slots,
                                   const float* inv_freq, float mscale, void* kv, int n_tokens, int n_q, int n_kv,
                                   int D, int rot_dim, int interleaved, int norm_dim, float eps, int page_size,
@@ -244,13 +344,27 @@ extern "C" int ss_rope_norm_cache(void* rows, int64_t row_stride, const int32_t*
         return (int)cudaErrorInvalidValue;
     const int heads = n_q + 2 * n_kv;
     const int warps = heads >= 8 ? 8 : (heads >= 4 ? 4 : 2);
+    const dim3 grid(n_tokens, (heads + warps - 1) / warps);
     const int64_t pool = num_pages * page_size;
+    if (dtype == SS_BF16 && (interleaved || rot_dim == 0) && D % 8 == 0 && row_stride % 8 == 0 && rot_dim <= 256 &&
+        ((uintptr_t)rows & 15) == 0 && ((uintptr_t)kv & 15) == 0) {
+        const int lph = D <= 32 ? 4 : (D <= 64 ? 8 : (D <= 128 ? 16 : 32));
+#define RN_GO(LPH)                                                                                                      \
+    ss_launch(rope_norm_cache_bf16x8_kernel<LPH>, dim3(n_tokens), dim3(256), 0, stream, (bf16*)rows, row_stride, positions, \
+              slots, inv_freq, mscale, (bf16*)kv, n_q, n_kv, D, rot_dim, norm_dim, eps, page_size, pool, write_cache, err)
+        if (lph == 4) RN_GO(4);
+        else if (lph == 8) RN_GO(8);
+        else if (lph == 16) RN_GO(16);
+        else RN_GO(32);
+#undef RN_GO
+        return SS_LAUNCH_CHECK();
+    }
     if (dtype == SS_BF16)
-        ss_launch(rope_norm_cache_kernel<bf16>, dim3(n_tokens), dim3(warps * 32), 0, stream, (bf16*)rows, row_stride,
+        ss_launch(rope_norm_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)rows, row_stride,
                   positions, slots, inv_freq, mscale, (bf16*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps,
                   page_size, pool, write_cache, err);
     else
-        ss_launch(rope_norm_cache_kernel<float>, dim3(n_tokens), dim3(warps * 32), 0, stream, (float*)rows, row_stride,
+        ss_launch(rope_norm_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)rows, row_stride,
                   positions, slots, inv_freq, mscale, (float*)kv, n_q, n_kv, D, rot_dim, interleaved, norm_dim, eps,
                   page_size, pool, write_cache, err);
     return SS_LAUNCH_CHECK();
