@@ -117,6 +117,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+#define TC_HC_MAX 4  // most hyper-connected streams a product writes into itself
+
 struct GemmArgs {
     void* C;            // output [M, N] (or [N, M] rows when swapped), bfloat16 or float32
     const void* bias;   // per output feature, or null
@@ -149,6 +151,12 @@ struct GemmArgs {
     float in_eps;
     // the constants of the fused gated unit (common.cuh: glu_mul); 1, 0, 0 is SwiGLU
     float act_alpha, act_limit, act_shift;
+    // hc_streams S > 0 (with `residual`): the stream is S hyper-connected streams, residual [N][S][M].  The product y
+    // (rounded to bfloat16) is WRITTEN into them, stream t <- sum_s hc_mix[s][t] * stream s + hc_out[t] * y, and the
+    // norm behind it READS u = sum_t hc_in[t] * stream t: scaled and tile_squares are formed from u.  The arithmetic
+    // is the hyper-connection kernel's, operation for operation.
+    int hc_streams;
+    float hc_mix[TC_HC_MAX * TC_HC_MAX], hc_out[TC_HC_MAX], hc_in[TC_HC_MAX];
 };
 
 __device__ __forceinline__ float bias_at(const GemmArgs& g, int f) {
@@ -306,7 +314,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         pdl_wait();  // the output, the scratch and the counters may still be in use by earlier kernels
         if (ENDS == 1) {
             const int c0 = (int)cluster_rank() + quarter * n_sl;
-            if (c0 < min(BN, g.N - n0)) res0 = *reinterpret_cast<const float4*>(g.residual + (int64_t)(n0 + c0) * g.M + m0 + lane * 4);
+            if (g.hc_streams == 0 && c0 < min(BN, g.N - n0))
+                res0 = *reinterpret_cast<const float4*>(g.residual + (int64_t)(n0 + c0) * g.M + m0 + lane * 4);
         }
         if constexpr (ENDS == 2) {
             // 1 / rms of every token of the tile, while the products run: a warp takes tokens quarter, quarter + 4,
@@ -471,13 +480,42 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         // (M is a multiple of 128.)  The stream takes this part of the branch's output, rounded as
                         // the output would have been; the norm behind it gets the stream times its weights, and
                         // the squares of the tile's 128 features in one sum
-                        float* res = g.residual + (int64_t)n * g.M + m;
-                        float4 x = i == q ? res0 : *reinterpret_cast<const float4*>(res);
-                        x.x = __fadd_rn(x.x, to_float(__float2bfloat16_rn(acc.x + bias4.x)));
-                        x.y = __fadd_rn(x.y, to_float(__float2bfloat16_rn(acc.y + bias4.y)));
-                        x.z = __fadd_rn(x.z, to_float(__float2bfloat16_rn(acc.z + bias4.z)));
-                        x.w = __fadd_rn(x.w, to_float(__float2bfloat16_rn(acc.w + bias4.w)));
-                        *reinterpret_cast<float4*>(res) = x;
+                        float4 x;
+                        if (g.hc_streams == 0) {
+                            float* res = g.residual + (int64_t)n * g.M + m;
+                            x = i == q ? res0 : *reinterpret_cast<const float4*>(res);
+                            x.x = __fadd_rn(x.x, to_float(__float2bfloat16_rn(acc.x + bias4.x)));
+                            x.y = __fadd_rn(x.y, to_float(__float2bfloat16_rn(acc.y + bias4.y)));
+                            x.z = __fadd_rn(x.z, to_float(__float2bfloat16_rn(acc.z + bias4.z)));
+                            x.w = __fadd_rn(x.w, to_float(__float2bfloat16_rn(acc.w + bias4.w)));
+                            *reinterpret_cast<float4*>(res) = x;
+                        } else {
+                            const int S = g.hc_streams;
+                            float* res = g.residual + (int64_t)n * S * g.M + m;
+                            const float4 y = make_float4(to_float(__float2bfloat16_rn(acc.x + bias4.x)), to_float(__float2bfloat16_rn(acc.y + bias4.y)),
+                                                         to_float(__float2bfloat16_rn(acc.z + bias4.z)), to_float(__float2bfloat16_rn(acc.w + bias4.w)));
+                            float4 xs[TC_HC_MAX];
+#pragma unroll
+                            for (int s = 0; s < TC_HC_MAX; ++s)
+                                if (s < S) xs[s] = *reinterpret_cast<const float4*>(res + (int64_t)s * g.M);
+                            x = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int t = 0; t < TC_HC_MAX; ++t) {
+                                if (t >= S) break;
+                                const float wo = g.hc_out[t], wi = g.hc_in[t];
+                                float4 v = make_float4(__fmul_rn(wo, y.x), __fmul_rn(wo, y.y), __fmul_rn(wo, y.z), __fmul_rn(wo, y.w));
+#pragma unroll
+                                for (int s = 0; s < TC_HC_MAX; ++s) {
+                                    if (s < S) {
+                                        const float ms = g.hc_mix[s * S + t];
+                                        v.x = fmaf(ms, xs[s].x, v.x); v.y = fmaf(ms, xs[s].y, v.y);
+                                        v.z = fmaf(ms, xs[s].z, v.z); v.w = fmaf(ms, xs[s].w, v.w);
+                                    }
+                                }
+                                *reinterpret_cast<float4*>(res + (int64_t)t * g.M) = v;
+                                x.x = fmaf(wi, v.x, x.x); x.y = fmaf(wi, v.y, x.y); x.z = fmaf(wi, v.z, x.z); x.w = fmaf(wi, v.w, x.w);
+                            }
+                        }
                         const __nv_bfloat162 lo = __floats2bfloat162_rn(nw4.x * x.x, nw4.y * x.y), hi = __floats2bfloat162_rn(nw4.z * x.z, nw4.w * x.w);
                         uint2 packed;
                         packed.x = *reinterpret_cast<const uint32_t*>(&lo);
@@ -944,6 +982,8 @@ struct NormEnds {  // see GemmArgs: the output added to the float32 stream, the 
     int in_tiles = 0;
     float in_eps = 0.f;
     float act_alpha = 1.f, act_limit = 0.f, act_shift = 0.f;  // the fused gated unit's constants (SwiGLU)
+    int hc_streams = 0;             // see GemmArgs
+    const float* hc_weights = nullptr;  // host memory: mix [S * S], out [S], in [S]
 };
 
 static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
@@ -973,6 +1013,14 @@ static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32
     g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
     g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
     g.act_alpha = ends.act_alpha; g.act_limit = ends.act_limit; g.act_shift = ends.act_shift;
+    g.hc_streams = 0;
+    if (ends.hc_streams > 0) {
+        const int S = ends.hc_streams;
+        if (S > TC_HC_MAX || !ends.residual || !ends.hc_weights) return -2010;
+        g.hc_streams = S;
+        for (int i = 0; i < S * S; ++i) g.hc_mix[i] = ends.hc_weights[i];
+        for (int i = 0; i < S; ++i) { g.hc_out[i] = ends.hc_weights[S * S + i]; g.hc_in[i] = ends.hc_weights[S * S + S + i]; }
+    }
     const bool deep = swapped && ((K + TC_BK - 1) / TC_BK + slices - 1) / slices >= 24;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
     if (!swapped) grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, slices);
@@ -1026,6 +1074,19 @@ extern "C" int ss_gemm_tc5_to_stream(const void* A, const void* B, const void* b
     return gemm_tc5(A, B, bias, bias_f32, nullptr, M, N, K, lda, ldb, M, bn, 1, 0, slices, 0, nullptr, nullptr, ends, err, stream);
 }
 
+// The same into S hyper-connected streams (see GemmArgs::hc_streams): streams [N, S, M]; hc_weights, in HOST memory,
+// holds mix [S * S] (from, to), out [S] and in [S].  scaled and tile_squares describe u = sum_t in[t] * stream t.
+extern "C" int ss_gemm_tc5_to_streams(const void* A, const void* B, const void* bias, int bias_f32, int M, int N, int K,
+                                      int64_t lda, int64_t ldb, int bn, int slices, float* streams, int n_streams,
+                                      const float* hc_weights, float* tile_squares, void* scaled, const void* norm_weight,
+                                      int norm_w_f32, int* err, cudaStream_t stream) {
+    NormEnds ends;
+    ends.residual = streams; ends.tile_squares = tile_squares; ends.scaled = scaled;
+    ends.norm_weight = norm_weight; ends.norm_w_f32 = norm_w_f32;
+    ends.hc_streams = n_streams; ends.hc_weights = hc_weights;
+    return gemm_tc5(A, B, bias, bias_f32, nullptr, M, N, K, lda, ldb, M, bn, 1, 0, slices, 0, nullptr, nullptr, ends, err, stream);
+}
+
 // The swapped product (bn 16) behind the RMS norm of that stream: B is `scaled`, and token n of the output is
 // multiplied, before the bias, by rsqrt(sum of in_squares[n][0 .. in_tiles) / K + eps); everything else as
 // ss_gemm_tc5.  Other shapes are refused with -2009.
@@ -1036,6 +1097,18 @@ extern "C" int ss_gemm_tc5_scaled(const void* A, const void* B, const float* in_
     NormEnds ends;
     ends.in_squares = in_squares; ends.in_tiles = in_tiles; ends.in_eps = eps;
     return gemm_tc5(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, bn, 1, out_f32, slices, swiglu, partial, counters,
+                    ends, err, stream);
+}
+
+// The same with the fused gated unit of other constants than SwiGLU's.
+extern "C" int ss_gemm_tc5_scaled_glu(const void* A, const void* B, const float* in_squares, int in_tiles, float eps,
+                                      const void* bias, int bias_f32, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                      int64_t ldc, int bn, int out_f32, int slices, float alpha, float limit, float shift,
+                                      float* partial, int* counters, int* err, cudaStream_t stream) {
+    NormEnds ends;
+    ends.in_squares = in_squares; ends.in_tiles = in_tiles; ends.in_eps = eps;
+    ends.act_alpha = alpha; ends.act_limit = limit; ends.act_shift = shift;
+    return gemm_tc5(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, bn, 1, out_f32, slices, 1, partial, counters,
                     ends, err, stream);
 }
 

@@ -95,6 +95,11 @@ _GEMM_SIGNATURES = {
                              c_float, c_float, c_float, c_void_p, c_void_p],
     "ss_gemm_tc5_to_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "ss_gemm_tc5_to_streams": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int,
+                               c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "ss_gemm_tc5_scaled_glu": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                               c_int64, c_int64, c_int64, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p,
+                               c_void_p, c_void_p],
     "ss_gemm_tc5_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                            c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -891,16 +896,21 @@ class PendingNorm:
     weight: torch.Tensor
     eps: float
     dtype: torch.dtype
+    # hyper-connected streams: ``stream`` is [tokens, S, hidden] and the norm is that of sum_t w_in[t] * stream t
+    # (``w_in`` None: the plain sum); ``scaled`` and ``squares`` describe that sum
+    w_in: torch.Tensor | None = None
 
     @property
     def shape(self) -> torch.Size:
-        return self.stream.shape
+        return self.scaled.shape
 
     @property
     def device(self) -> torch.device:
         return self.stream.device
 
     def materialize(self) -> torch.Tensor:
+        if self.stream.dim() == 3:
+            return hc_norm(self.stream, None, None, None, self.w_in, self.weight, self.eps, self.dtype)
         return add_rmsnorm(self.stream, None, self.weight, self.eps, self.dtype)
 
 
@@ -942,7 +952,7 @@ def _gemm_plan(tokens: int, features: int, k: int, sms: int) -> tuple[bool, int,
 def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None = None,
                  out_dtype: torch.dtype | None = None, plan: tuple[bool, int, int] | None = None,
                  swiglu: bool = False, to_stream: tuple[torch.Tensor, torch.Tensor] | None = None,
-                 glu: tuple[float, float, float] | None = None):
+                 glu: tuple[float, float, float] | None = None, hc: "np.ndarray | None" = None):
     """``x @ weight.T + bias`` for bfloat16 ``x`` [tokens, K] and ``weight`` [features, K] on the tcgen05 tensor
     cores (TMA-fed, accumulator in tensor memory); output bfloat16 or float32.  K must be a multiple of 8.
 
@@ -950,6 +960,9 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
     features; the result is ``silu(gate) * up`` with features / 2 columns, formed in the product's epilogue.
 
     ``glu`` = (alpha, limit, shift) with ``swiglu``: the fused unit is `glu_limited`'s instead of SwiGLU.
+    ``hc`` with ``to_stream``: the stream is [tokens, S, features], S hyper-connected streams (at most 4), and ``hc`` a
+    float32 host array of S * S + 2 S values, mix [from, to], out, in: the product is written into the streams as
+    `hc_norm` writes a branch output, and what comes back describes ``sum_t in[t] * stream t``.
 
     ``to_stream`` = (float32 stream [tokens, features], weights of the norm behind it), where `adds_to_stream`:
     the product, rounded to bfloat16, is added to the stream in place instead of being returned, and the function
@@ -994,13 +1007,28 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
         stream, norm_weight = to_stream
         _need(stream, torch.float32, "stream")
         _need(norm_weight, None, "norm weight")
-        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or tuple(stream.shape) != out_shape
+        n_streams = 0
+        if hc is not None:
+            n_streams = stream.shape[1] if stream.dim() == 3 else 0
+            if not 1 <= n_streams <= 4 or hc.dtype != np.float32 or hc.size != n_streams * (n_streams + 2) \
+                    or not hc.flags["C_CONTIGUOUS"]:
+                raise KernelError("hyper-connected streams: [tokens, S <= 4, features] and S * S + 2 S float32 weights")
+        stream_shape = (tokens, n_streams, features) if n_streams else out_shape
+        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or tuple(stream.shape) != stream_shape
                 or not (swapped and 2 <= slices <= 8 and tokens <= bn) or features % 128
                 or norm_weight.numel() != features or norm_weight.dtype not in (torch.float32, torch.bfloat16)):
             raise KernelError("a product into the stream needs its plain bfloat16 output, K slices in a cluster, a "
                               "width in steps of 128 and a stream of its shape")
         scaled = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
         squares = torch.empty((tokens, features // 128), dtype=torch.float32, device=x.device)
+        if n_streams:
+            rc = gemm_library().ss_gemm_tc5_to_streams(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, a.shape[0],
+                                                       b.shape[0], k, k, k, bn, slices, stream.data_ptr(), n_streams,
+                                                       hc.ctypes.data, squares.data_ptr(), scaled.data_ptr(),
+                                                       norm_weight.data_ptr(), int(norm_weight.dtype == torch.float32),
+                                                       error_word(x.device).data_ptr(), _stream())
+            _check(rc, "gemm_tcgen05 into hyper-connected streams")
+            return scaled, squares
         rc = gemm_library().ss_gemm_tc5_to_stream(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, a.shape[0], b.shape[0],
                                                   k, k, k, bn, slices, stream.data_ptr(), squares.data_ptr(),
                                                   scaled.data_ptr(), norm_weight.data_ptr(),
@@ -1011,6 +1039,17 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
     if pending is not None:
         if not swapped or bn != 16 or pending.weight.numel() != k or pending.squares.shape[0] != tokens:
             raise KernelError("a pending norm feeds the swapped product of at most 16 tokens, over the stream's whole width")
+        if glu is not None:
+            if not swiglu:
+                raise KernelError("the constants of a gated unit come with the fused gate/up epilogue")
+            rc = gemm_library().ss_gemm_tc5_scaled_glu(a.data_ptr(), b.data_ptr(), pending.squares.data_ptr(),
+                                                       pending.squares.shape[1], float(pending.eps), _ptr(bias), bias_f32,
+                                                       out.data_ptr(), a.shape[0], tokens, k, k, k, out.shape[1], bn,
+                                                       int(out_dtype == torch.float32), slices, float(glu[0]),
+                                                       float(glu[1]), float(glu[2]), _ptr(partial), _ptr(counters),
+                                                       error_word(x.device).data_ptr(), _stream())
+            _check(rc, "gemm_tcgen05 with a gated unit behind a pending norm")
+            return out
         rc = gemm_library().ss_gemm_tc5_scaled(a.data_ptr(), b.data_ptr(), pending.squares.data_ptr(),
                                                pending.squares.shape[1], float(pending.eps), _ptr(bias), bias_f32,
                                                out.data_ptr(), a.shape[0], tokens, k, k, k, out.shape[1], bn,
@@ -1233,6 +1272,23 @@ def linear_add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     return add_rmsnorm(residual, linear(x, weight, bias), norm_weight, eps, out_dtype)
 
 
+def linear_hc_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, streams: torch.Tensor,
+                      mix: torch.Tensor, w_out: torch.Tensor, w_in: torch.Tensor | None, hc_host: "np.ndarray | None",
+                      norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> "torch.Tensor | PendingNorm":
+    """`linear_add_rmsnorm` for hyper-connected streams [tokens, S, hidden]: ``y = x @ weight.T + bias`` is written
+    into the streams with the branch's ``mix`` and ``w_out``, and the norm of ``sum_t w_in[t] * stream t`` comes back
+    (see `hc_norm`).  With few bfloat16 tokens and at most 4 streams the product does the write in its epilogue
+    (``hc_host``: the same weights as a float32 host array, mix, out, in) and the norm comes back as a
+    `PendingNorm`; everything else is `linear` followed by `hc_norm`."""
+    tokens, n_streams, hidden = streams.shape
+    if hc_host is not None and tokens > 0 and n_streams <= 4 and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 \
+            and weight.shape[0] == hidden and norm_weight.numel() == hidden and x.shape[0] <= SMALL_BATCH \
+            and adds_to_stream(tokens, hidden, x.shape[1], sm_count(x.device)):
+        scaled, squares = gemm_tcgen05(x, weight, bias, to_stream=(streams, norm_weight), hc=hc_host)
+        return PendingNorm(streams, scaled, squares, norm_weight, eps, out_dtype, w_in=w_in)
+    return hc_norm(streams, linear(x, weight, bias), mix, w_out, w_in, norm_weight, eps, out_dtype)
+
+
 def many_tokens_swiglu_fits(tokens: int, features: int, sms: int | None = None) -> bool:
     """Where the persistent tcgen05 kernel with its fused SwiGLU epilogue is at least as fast as the library
     product followed by the SwiGLU kernel: enough 256 x 256 tiles to keep every pair of SMs busy for several
@@ -1267,6 +1323,9 @@ def gate_up_glu(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: tor
     portions; runs of 64) this does the same with the unit's constants; everything else is the stacked product
     followed by the activation kernel."""
     if isinstance(x, PendingNorm):
+        if (block == 64 and weight.shape[0] % 128 == 0 and x.shape[0] <= CLUSTER_BATCH
+                and takes_pending_norm(x, weight.shape[0], swiglu=True)):
+            return gemm_tcgen05(x, weight, bias, swiglu=True, glu=(alpha, limit, shift))
         x = x.materialize()
     if x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0 and x.shape[1] % 8 == 0:
         sms = sm_count(x.device)
@@ -1287,6 +1346,6 @@ def set_programmatic_launch(enabled: bool) -> None:
     _state["pdl"] = bool(enabled)
 
 
-__all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_norm", "rope_norm_cache", "glu_limited", "gate_up_glu", "sigmoid_gate", "key_span", "rope_and_cache", "swiglu",
+__all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_norm", "linear_hc_rmsnorm", "rope_norm_cache", "glu_limited", "gate_up_glu", "sigmoid_gate", "key_span", "rope_and_cache", "swiglu",
            "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

@@ -20,11 +20,12 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from slipstream_b200 import ops
 
-from .base import BLOCKS, NORMS, Block, FeedForward, LayerBinding, Mixer, Norm, Part, Runtime, WeightSpec
+from .base import BLOCKS, NORMS, Block, FeedForward, IntoNorm, LayerBinding, Mixer, Norm, Part, Runtime, WeightSpec, settle
 
 
 @dataclass
@@ -34,6 +35,17 @@ class StreamWrite:
     y: torch.Tensor
     mix: torch.Tensor  # float32 [S, S], [from, to]
     out: torch.Tensor  # float32 [S]
+
+
+@dataclass
+class IntoStreams(IntoNorm):
+    """`IntoNorm` for hyper-connected streams: the branch's last projection is written into the streams with the
+    weights of ``writer`` (the branch's own norm) and ``norm`` (the next branch's) reads and norms what results."""
+
+    writer: "ConnectedNorm" = None
+
+    def close(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None):
+        return self.norm.write_linear_then_norm(self.residual, x, weight, bias, self.writer)
 
 
 @NORMS.register("connected_rmsnorm")
@@ -76,6 +88,10 @@ class ConnectedNorm(Norm):
             self.w_in = None
             self.w_out = torch.ones(s, dtype=torch.float32, device=dev)
             self.mix = torch.eye(s, dtype=torch.float32, device=dev)
+        # the same weights on the host: a product that writes into the streams itself takes them as launch arguments
+        self.host_write = np.concatenate([self.mix.cpu().numpy().reshape(-1), self.w_out.cpu().numpy().reshape(-1)])
+        self.host_in = self.w_in.cpu().numpy().reshape(-1) if self.w_in is not None else np.ones(s, dtype=np.float32)
+        self._fused: dict[int, np.ndarray] = {}
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
@@ -95,6 +111,18 @@ class ConnectedNorm(Norm):
             return ops.hc_norm(streams, None, None, None, self.w_in, self.weight, self.eps, self.runtime.dtype, rows=rows)
         return ops.hc_norm(streams, delta.y, delta.mix, delta.out, self.w_in, self.weight, self.eps, self.runtime.dtype,
                            rows=rows)
+
+    def write_linear_then_norm(self, residual: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                               bias: torch.Tensor | None, writer: "ConnectedNorm"):
+        """``add_norm(residual, writer.write_of(x @ weight.T + bias))``: a branch's last projection, its write into the
+        streams and this norm's read; may come back as an ``ops.PendingNorm`` (see `ops.linear_hc_rmsnorm`)."""
+        streams = residual if residual.dim() == 3 else residual.view(residual.shape[0], 1, residual.shape[1])
+        host = self._fused.get(id(writer))
+        if host is None:
+            host = self._fused[id(writer)] = np.ascontiguousarray(
+                np.concatenate([writer.host_write, self.host_in]).astype(np.float32))
+        return ops.linear_hc_rmsnorm(x, weight, bias, streams, writer.mix, writer.w_out, self.w_in, host, self.weight,
+                                     self.eps, self.runtime.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.add_norm(x, None)
@@ -125,9 +153,30 @@ class HyperConnectionBlock(Block):
 
     def forward(self, residual: torch.Tensor, pending: "StreamWrite | None", ctx,
                 layer: LayerBinding) -> "tuple[torch.Tensor, StreamWrite]":
-        x = self.mixer_norm.add_norm(residual, pending)
-        pending = self.mixer_norm.write_of(self.mixer.forward(x, ctx, layer))
-        if self.feed_forward is None:
-            return residual, pending
-        x = self.ffn_norm.add_norm(residual, pending)
-        return residual, self.ffn_norm.write_of(self.feed_forward.forward(x, ctx))
+        residual, pending, _ = self.forward_chained(residual, pending, None, None, ctx, layer)
+        return residual, pending
+
+    def first_norm(self) -> Norm:
+        return self.mixer_norm
+
+    def forward_chained(self, residual: torch.Tensor, pending: "StreamWrite | None", normed, following: Norm | None, ctx,
+                        layer: LayerBinding):
+        """A branch whose last operation is a projection hands that projection, its write into the streams and the
+        next norm to one call (`IntoStreams`); the next norm is this block's second one, the next block's first one
+        (``following``) or the model's last one."""
+        chain = following if isinstance(following, ConnectedNorm) else None
+        x = settle(normed, self.mixer) if normed is not None else self.mixer_norm.add_norm(residual, pending)
+        after_mixer = self.ffn_norm if self.feed_forward is not None else chain
+        if self.mixer.takes_into and after_mixer is not None:
+            x = self.mixer.forward(x, ctx, layer, into=IntoStreams(after_mixer, residual, self.mixer_norm))
+            if self.feed_forward is None:
+                return residual, None, x
+            x = settle(x, self.feed_forward)
+        else:
+            pending = self.mixer_norm.write_of(self.mixer.forward(x, ctx, layer))
+            if self.feed_forward is None:
+                return residual, pending, None
+            x = self.ffn_norm.add_norm(residual, pending)
+        if chain is not None and self.feed_forward.takes_into:
+            return residual, None, self.feed_forward.forward(x, ctx, into=IntoStreams(chain, residual, self.ffn_norm))
+        return residual, self.ffn_norm.write_of(self.feed_forward.forward(x, ctx)), None

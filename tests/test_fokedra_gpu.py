@@ -64,6 +64,14 @@ def configs():
               "layers": [layer(2, 2, 64, 64, 0.25, rot(32, 1000.0), ff=64),
                          layer(3, 1, 16, 8, 1.0, None, chunk=32, ff=32, limit=0.5),
                          layer(2, 1, 16, 16, 1.0, rot(16, 10.0), chunk=1)]},
+        # four streams over a width in steps of 128: in bfloat16 decode steps the o and down products write into the
+        # streams themselves; a layer without feed-forward in the middle and at the end of the chain
+        "T": {"architecture": "Fokedra", "vocab": 150, "width": 256, "streams": 4, "norm": {"eps": 1e-6},
+              "embedding": {"scale": 3.0},
+              "layers": [layer(4, 2, 32, 32, 0.4, rot(32, 10000.0, yarn), chunk=24, ff=128),
+                         layer(4, 2, 32, 32, 0.4, rot(32, 10000.0, yarn), chunk=24, kv_from=0),
+                         layer(4, 4, 32, 32, 0.4, rot(16, 10000.0), ff=256, limit=1.5),
+                         layer(8, 1, 32, 32, 0.3, rot(32, 10000.0))]},
     }
 
 
@@ -363,6 +371,39 @@ def test_gated_unit_in_the_products_epilogue(tokens, inter, k):
     assert got.shape == want.shape and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("s, tokens, hidden, k", [(1, 3, 128, 512), (2, 8, 256, 128), (3, 16, 384, 1024), (4, 1, 128, 256),
+                                                 (3, 5, 192, 256), (5, 4, 128, 256), (2, 40, 128, 256)])
+def test_a_products_write_into_the_streams(s, tokens, hidden, k):
+    """A branch's last projection with the write into the streams and the next read + norm: inside the product where
+    it can (few bfloat16 tokens, at most 4 streams, a width in steps of 128), else product then kernel; either way
+    the streams, the norm (as a tensor, or pending and then finished by hand or by the next product) are the plain ones."""
+    from slipstream_b200 import ops
+    g = torch.Generator().manual_seed(s * 1000 + hidden)
+    x = torch.randn(tokens, k, generator=g).bfloat16()
+    w = (torch.randn(hidden, k, generator=g) * k ** -0.5).bfloat16()
+    streams = torch.randn(tokens, s, hidden, generator=g)
+    mix, w_out, w_in = torch.randn(s, s, generator=g), torch.randn(s, generator=g), torch.randn(s, generator=g)
+    weight = (1.0 + 0.1 * torch.randn(hidden, generator=g)).bfloat16()
+    host = torch.cat([mix.reshape(-1), w_out, w_in]).numpy().copy()
+    y = (x.double() @ w.double().T).bfloat16().double()  # the branch output is rounded to bfloat16 before it is written
+    want_streams = plain.hyper_write(streams.double().transpose(0, 1), y, mix.double(), w_out.double())
+    want = plain.rms_norm(plain.hyper_read(want_streams, w_in.double()), weight.double(), 1e-6)
+    dev = streams.to(DEV)
+    got = ops.linear_hc_rmsnorm(x.to(DEV), w.to(DEV), None, dev, mix.to(DEV), w_out.to(DEV), w_in.to(DEV), host,
+                                weight.to(DEV), 1e-6, torch.bfloat16)
+    fused = isinstance(got, ops.PendingNorm)
+    assert fused == (s <= 4 and tokens <= 16 and hidden % 128 == 0)
+    assert torch.allclose(dev.cpu().double().transpose(0, 1), want_streams, atol=2e-2, rtol=1e-2)
+    if fused:
+        # the next product finishes the norm: against the plain norm times a matrix
+        w2 = (torch.randn(256, hidden, generator=g) * hidden ** -0.5).bfloat16()
+        out = ops.linear(got, w2.to(DEV)).cpu().double()
+        assert torch.allclose(out, want @ w2.double().T, atol=4e-2, rtol=2e-2)
+        got = got.materialize()
+    assert torch.allclose(got.cpu().double(), want, atol=4e-2, rtol=2e-2)
+
+
 def chunked_attention_plain(q, k, v, chunk, scale):
     """q [n, H, d] at the LAST n of the m positions of k, v [m, G, d]."""
     n, H, _ = q.shape
@@ -442,7 +483,7 @@ def test_chunked_visibility_in_every_attention_kernel(d, page, chunk, lens, q_le
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "T"])
 def test_every_way_of_cutting_gives_the_plain_logits(models, name, dtype):
     """Whole prompts, token-by-token decoding from the first token on, portions down to two tokens, and unequal
     requests side by side while others come and go, in a pool that holds less than the requests need in total."""
@@ -471,7 +512,7 @@ def test_every_way_of_cutting_gives_the_plain_logits(models, name, dtype):
 def test_long_decoding_crosses_chunks_and_pages(models, dtype):
     """A short prompt and 150 decoded tokens (captured decode steps), beside a second request that joins and leaves:
     every chunk edge of 7, 16, 32 and 40 and every page edge of 8 is crossed in decoding."""
-    for name in ("P", "Q", "R"):
+    for name in ("P", "Q", "R", "T"):
         folder, config, weights = models[name]
         reqs = {"a": tokens_of(config["vocab"], 160, 7), "b": tokens_of(config["vocab"], 60, 8)}
         want = {k: plain_logits(name, config, weights, v) for k, v in reqs.items()}
