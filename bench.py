@@ -415,6 +415,7 @@ def run_compare(args) -> int:
             runner.release(f"p{w}")
             times.append(start.elapsed_time(stop))
         prefill_ms = sorted(times[-5:])[2]
+        print(f"[bench]   prefill {prefill_ms:.3f} ms", file=sys.stderr, flush=True)
         # decode: `batch` requests behind `ctx_tokens` cached tokens each
         ids = [f"d{i}" for i in range(batch)]
         per_step = max(1, 4096 // ctx_tokens)
@@ -445,9 +446,16 @@ def run_compare(args) -> int:
 
     for name in (args.sizes.split(",") if args.sizes else COMPARE_SIZES):
         qwen, fokedra = compare_configs(COMPARE_SIZES[name], args.mask_chunk, args.streams, args.share_kv)
-        result["sizes"][name] = {"qwen2": measure(qwen), "fokedra": measure(fokedra)}
+        result["sizes"][name] = {}
+        for which, config in (("qwen2", qwen), ("fokedra", fokedra)):
+            if which == "qwen2" and args.skip_qwen2:
+                continue
+            print(f"[bench] {name} {which} ...", file=sys.stderr, flush=True)
+            result["sizes"][name][which] = measure(config)
+            print(f"[bench] {name} {which}: {result['sizes'][name][which]}", file=sys.stderr, flush=True)
 
     # ---- every kernel the design adds, beside the like kernel of the Qwen2.5 path, at the 7B layer sizes
+    print("[bench] single kernels ...", file=sys.stderr, flush=True)
     z = COMPARE_SIZES["7b"]
     h, n_q, n_kv, d, inter, S = z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"], args.streams
     gen = torch.Generator(device=dev).manual_seed(1)
@@ -592,6 +600,7 @@ def main() -> int:
     ap.add_argument("--sizes", default="", help="--compare: which of 0.5b,7b,14b (default: all)")
     ap.add_argument("--mask-chunk", type=int, default=8192, help="--compare: positions per attention chunk")
     ap.add_argument("--streams", type=int, default=2, help="--compare: residual streams")
+    ap.add_argument("--skip-qwen2", action="store_true", help="--compare: time the other design only")
     ap.add_argument("--share-kv", action="store_true", help="--compare: every second layer reads the pages of the layer before")
     ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention"], default=None,
                     help="run just this part and print a short line (for profiling); gemm / attention: tables of "

@@ -7,6 +7,12 @@
 
 #include "common.cuh"
 
+// None of these kernels lets the kernel behind it start early (griddepcontrol.launch_dependents): each is short, and
+// with the early start a prompt step of 2,048 tokens at a width of 5,120 (every second launch a two-SM tcgen05
+// product or the tcgen05 attention, which take tensor memory before they wait for the kernel in front) stopped
+// making progress about three times in four; with the kernels of this file in stream order it did not in any run.
+// They still wait for the kernel in front (griddepcontrol.wait), which may have started them early.
+
 // ---------------------------------------------------------------- hyper-connections
 //
 // A token has S streams x_0 .. x_{S-1} of `hidden` floats (streams: [tokens][S][hidden]).  One launch does, per token,
@@ -24,7 +30,6 @@ __global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict_
                                const float* __restrict__ w_out, const float* __restrict__ w_in,
                                const void* __restrict__ weight, int w_f32, T* __restrict__ out,
                                const int32_t* __restrict__ rows, int S, int hidden, float eps) {
-    pdl_launch_dependents();
     // the connection weights are constants of the model: read before the wait for the kernel in front
     float m[SMAX][SMAX], wo[SMAX], wi[SMAX];
 #pragma unroll
@@ -156,7 +161,6 @@ rope_norm_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* 
                        const int32_t* __restrict__ slots, const float* __restrict__ inv_freq, float mscale,
                        T* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim, int interleaved, int norm_dim,
                        float eps, int page_size, int64_t pool_slots, int write_cache, int* err) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float cos_s[128], sin_s[128];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -244,7 +248,6 @@ rope_norm_cache_bf16x8_kernel(bf16* __restrict__ rows, int64_t row_stride, const
                               const int32_t* __restrict__ slots, const float* __restrict__ inv_freq, float mscale,
                               bf16* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim, int norm_dim, float eps,
                               int page_size, int64_t pool_slots, int write_cache, int* err) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float cos_s[128], sin_s[128];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -380,7 +383,6 @@ extern "C" int ss_rope_norm_cache(void* rows, int64_t row_stride, const int32_t*
 template <typename T>
 __global__ void glu_limited_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter, int block,
                                    float alpha, float limit, float shift) {
-    pdl_launch_dependents();
     pdl_wait();
     const int64_t total = n * inter;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -395,7 +397,6 @@ __global__ void glu_limited_kernel(const T* __restrict__ in, T* __restrict__ out
 // bfloat16, 8 gate and the 8 matching up features per thread (block % 8 == 0, 16-byte aligned rows).
 __global__ void glu_limited_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int64_t n, int inter,
                                           int block, float alpha, float limit, float shift) {
-    pdl_launch_dependents();
     pdl_wait();
     const int per_row = inter / 8;
     const int64_t total = n * per_row;
@@ -450,7 +451,6 @@ extern "C" int ss_glu_limited(const void* in, void* out, int64_t n, int inter, i
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, int64_t x_stride, const T* __restrict__ gate, int64_t gate_stride,
                                     int64_t n, int width) {
-    pdl_launch_dependents();
     pdl_wait();
     const int64_t total = n * width;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
