@@ -54,9 +54,9 @@ def configs():
         # no streams key (the plain residual sum); heads of 64 on one kv head under chunks of 40 (the TMA-fed decode
         # kernel with a lower bound on the keys); two readers of one layer's pages
         "Q": {"architecture": "Fokedra", "vocab": 131, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
-              "layers": [layer(8, 1, 64, 64, 0.3, rot(64, 250000.0, (2.0, 128, 16.0, 1.0)), chunk=40, ff=128),
-                         layer(8, 1, 64, 64, 0.3, rot(64, 250000.0, (2.0, 128, 16.0, 1.0)), chunk=40, kv_from=0, ff=64),
-                         layer(8, 1, 64, 64, 0.2, rot(64, 250000.0, (2.0, 128, 16.0, 1.0)), kv_from=0, ff=64)]},
+              "layers": [layer(8, 1, 64, 64, 0.3, rot(64, 300000.0, (3.0, 128, 16.0, 1.0)), chunk=40, ff=128),
+                         layer(8, 1, 64, 64, 0.3, rot(64, 300000.0, (3.0, 128, 16.0, 1.0)), chunk=40, kv_from=0, ff=64),
+                         layer(8, 1, 64, 64, 0.2, rot(64, 300000.0, (3.0, 128, 16.0, 1.0)), kv_from=0, ff=64)]},
         # one stream WITH connection weights; heads of 64 without any mask (the tcgen05 prefill kernel); a layer
         # without rotation; values narrower than keys; chunks of one token and chunks of a page multiple
         "R": {"architecture": "Fokedra", "vocab": 96, "width": 96, "streams": 1, "norm": {"eps": 1e-6},
@@ -222,7 +222,7 @@ def test_model_structure_follows_the_configuration():
 
 def test_stretched_frequencies_equal_the_plain_table():
     from slipstream_b200.parts import RotaryEncoding, YarnRotaryEncoding
-    for dims, base, scaling in ((16, 5000.0, (4.0, 64, 8.0, 0.5)), (64, 250000.0, (2.0, 128, 16.0, 1.0)),
+    for dims, base, scaling in ((16, 5000.0, (4.0, 64, 8.0, 0.5)), (64, 300000.0, (3.0, 128, 16.0, 1.0)),
                                 (48, 10000.0, (8.0, 4096, 32.0, 1.0)), (8, 50.0, (3.0, 16, 1.0, 0.9))):
         f, m = plain.rotary_frequencies(rot(dims, base, scaling))
         enc = YarnRotaryEncoding(dims + 16, base, dims, interleaved=True, factor=scaling[0], original=scaling[1],
@@ -254,7 +254,7 @@ def test_chunked_groups_give_pages_back_at_chunk_edges():
 # --------------------------------------------------------------------------- mechanisms alone
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("s, hidden", [(1, 40), (2, 192), (3, 64), (4, 1030), (6, 96)])
+@pytest.mark.parametrize("s, hidden", [(1, 40), (2, 176), (3, 64), (4, 1030), (6, 96)])
 def test_hyper_connection_step(s, hidden):
     from slipstream_b200 import ops
     g = torch.Generator().manual_seed(s * 100 + hidden)
@@ -355,7 +355,7 @@ def test_limited_gated_unit_and_sigmoid_gate(dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tokens, inter, k", [(5, 256, 192), (16, 1024, 64), (2048, 9472, 128), (40, 128, 72)])
+@pytest.mark.parametrize("tokens, inter, k", [(5, 256, 200), (16, 1024, 64), (2048, 9472, 128), (40, 128, 72)])
 def test_gated_unit_in_the_products_epilogue(tokens, inter, k):
     """Few tokens (the streaming product), many tokens and features (the two-SM product) and a case that takes
     the product followed by the activation kernel: all against the plain formula on the bfloat16 inputs."""
@@ -373,7 +373,7 @@ def test_gated_unit_in_the_products_epilogue(tokens, inter, k):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("s, tokens, hidden, k", [(1, 3, 128, 512), (2, 8, 256, 128), (3, 16, 384, 1024), (4, 1, 128, 256),
-                                                 (3, 5, 192, 256), (5, 4, 128, 256), (2, 40, 128, 256)])
+                                                 (3, 5, 320, 256), (5, 4, 128, 256), (2, 40, 128, 256)])
 def test_a_products_write_into_the_streams(s, tokens, hidden, k):
     """A branch's last projection with the write into the streams and the next read + norm: inside the product where
     it can (few bfloat16 tokens, at most 4 streams, a width in steps of 128), else product then kernel; either way
@@ -418,11 +418,11 @@ def chunked_attention_plain(q, k, v, chunk, scale):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("d, page, chunk, lens, q_lens", [
-    (48, 16, 120, (121, 240, 119, 361), (1, 1, 1, 1)),      # decode: just behind, at and in front of an edge
+    (48, 16, 110, (111, 220, 109, 331), (1, 1, 1, 1)),      # decode: just behind, at and in front of an edge
     (64, 16, 40, (81, 80, 79, 200), (1, 1, 1, 1)),          # the TMA-fed decode kernel with a lower bound
     (64, 8, 40, (90, 130, 41), (50, 130, 2)),               # prompt portions across edges
     (128, 16, 100, (700, 333, 64), (300, 333, 1)), (64, 32, 64, (640,), (640,)), (64, 16, 1000, (300, 90), (300, 2)),
-    (32, 4, 7, (30, 64, 15), (9, 64, 15)), (16, 16, 1, (20, 5), (20, 1)), (48, 16, 120, (500,), (260,))])
+    (32, 4, 7, (30, 64, 15), (9, 64, 15)), (16, 16, 1, (20, 5), (20, 1)), (48, 16, 110, (500,), (260,))])
 def test_chunked_visibility_in_every_attention_kernel(d, page, chunk, lens, q_lens):
     from slipstream_b200 import ops
     from slipstream_b200.engine.context import query_tiles_host
