@@ -72,6 +72,12 @@ def configs():
                          layer(4, 2, 32, 32, 0.4, rot(32, 10000.0, yarn), chunk=24, kv_from=0),
                          layer(4, 4, 32, 32, 0.4, rot(16, 10000.0), ff=256, limit=1.5),
                          layer(8, 1, 32, 32, 0.3, rot(32, 10000.0))]},
+        # a width and a vocabulary that are multiples of 8 and of nothing more, keys of 80 elements with values of 16,
+        # five heads with kv heads of their own, two streams, chunks that are no multiple of a page
+        "U": {"architecture": "Fokedra", "vocab": 1003, "width": 104, "streams": 2, "norm": {"eps": 1e-6},
+              "embedding": {"scale": 10.2},
+              "layers": [layer(5, 5, 80, 16, 0.2, rot(40, 20000.0, (8.0, 32, 4.0, 2.0)), chunk=50, ff=72, limit=2.0),
+                         layer(5, 5, 80, 16, 0.2, rot(40, 20000.0, (8.0, 32, 4.0, 2.0)), chunk=50, kv_from=0, ff=136)]},
     }
 
 
@@ -483,7 +489,7 @@ def test_chunked_visibility_in_every_attention_kernel(d, page, chunk, lens, q_le
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "T"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "T", "U"])
 def test_every_way_of_cutting_gives_the_plain_logits(models, name, dtype):
     """Whole prompts, token-by-token decoding from the first token on, portions down to two tokens, and unequal
     requests side by side while others come and go, in a pool that holds less than the requests need in total."""
