@@ -99,10 +99,121 @@ __global__ void hc_norm_kernel(float* __restrict__ streams, const T* __restrict_
     }
 }
 
+// Four consecutive elements with one access.
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const bf16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void st4(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const uint32_t*>(&a);
+    t.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// The same step with 16-byte accesses and the row walked ONCE (hidden a multiple of 4, at most 16 * blockDim): a
+// thread keeps its up to NV groups of four values of u in registers between the sum of squares and the output.  The
+// arithmetic behind every value is the kernel's above, operation for operation.
+#define HC_NV 4
+template <typename T, int SMAX>
+__global__ void hc_norm_vec_kernel(float* __restrict__ streams, const T* __restrict__ y, const float* __restrict__ mix,
+                                   const float* __restrict__ w_out, const float* __restrict__ w_in,
+                                   const void* __restrict__ weight, int w_f32, T* __restrict__ out,
+                                   const int32_t* __restrict__ rows, int S, int hidden, float eps) {
+    float m[SMAX][SMAX], wo[SMAX], wi[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) {
+        wo[s] = (y != nullptr && s < S) ? w_out[s] : 0.f;
+        wi[s] = s < S ? (w_in ? w_in[s] : 1.f) : 0.f;
+#pragma unroll
+        for (int t = 0; t < SMAX; ++t) m[s][t] = (y != nullptr && s < S && t < S) ? mix[s * S + t] : 0.f;
+    }
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* base = streams + src * (int64_t)S * hidden;
+    const T* yr = y ? y + src * (int64_t)hidden : nullptr;
+    const bool write_back = rows == nullptr && y != nullptr;
+    float u[HC_NV][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < HC_NV; ++it) {
+        const int j = (threadIdx.x + it * blockDim.x) * 4;
+        if (j >= hidden) break;
+        float x[SMAX][4];
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+            if (s < S) ld4(base + (int64_t)s * hidden + j, x[s]);
+        u[it][0] = u[it][1] = u[it][2] = u[it][3] = 0.f;
+        if (yr) {
+            float yv[4];
+            ld4(yr + j, yv);
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                if (t >= S) break;
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = __fmul_rn(wo[t], yv[e]);
+#pragma unroll
+                for (int s = 0; s < SMAX; ++s) {
+                    if (s < S) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = fmaf(m[s][t], x[s][e], v[e]);
+                    }
+                }
+                if (write_back) st4(base + (int64_t)t * hidden + j, v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) u[it][e] = fmaf(wi[t], v[e], u[it][e]);
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < SMAX; ++t) {
+                if (t < S) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) u[it][e] = fmaf(wi[t], x[t][e], u[it][e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss = fmaf(u[it][e], u[it][e], ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    T* o = out + (int64_t)blockIdx.x * hidden;
+#pragma unroll
+    for (int it = 0; it < HC_NV; ++it) {
+        const int j = (threadIdx.x + it * blockDim.x) * 4;
+        if (j >= hidden) break;
+        float r[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r[e] = u[it][e] * rstd * load_vec<T>(weight, j + e, w_f32);
+        st4(o + j, r);
+    }
+}
+
 template <typename T>
 static int launch_hc_norm(float* streams, const void* y, const float* mix, const float* w_out, const float* w_in,
                           const void* weight, int w_f32, void* out, const int32_t* rows, int n_rows, int S, int hidden,
                           float eps, cudaStream_t stream) {
+    if (hidden % 4 == 0 && hidden <= 16 * 512 && S <= 4) {
+        int vthreads = ((hidden / 4 + HC_NV - 1) / HC_NV + 31) / 32 * 32;
+        vthreads = vthreads < 64 ? 64 : vthreads;
+#define HC_VEC(SMAX)                                                                                                     \
+    ss_launch(hc_norm_vec_kernel<T, SMAX>, dim3(n_rows), dim3(vthreads), 0, stream, streams, (const T*)y, mix, w_out, w_in, \
+              weight, w_f32, (T*)out, rows, S, hidden, eps)
+        if (S == 1) HC_VEC(1);
+        else if (S == 2) HC_VEC(2);
+        else HC_VEC(4);
+#undef HC_VEC
+        return SS_LAUNCH_CHECK();
+    }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
 #define HC_GO(SMAX)                                                                                                   \
     ss_launch(hc_norm_kernel<T, SMAX>, dim3(n_rows), dim3(threads), 0, stream, streams, (const T*)y, mix, w_out, w_in, \

@@ -15,7 +15,7 @@ from __future__ import annotations
 
 from slipstream_b200.config.fokedra_config import FokedraConfig, RotaryConfig
 from slipstream_b200.parts import (ConnectedNorm, HyperConnectionBlock, LMHead, NoPositionEncoding, PagedAttention,
-                                   RotaryEncoding, SwiGLUFeedForward, TokenEmbedding, YarnRotaryEncoding)
+                                   RotaryEncoding, GatedFeedForward, TokenEmbedding, YarnRotaryEncoding)
 
 from .decoder import DecoderLM, ExecEntry
 
@@ -50,9 +50,9 @@ def build_fokedra(config: FokedraConfig) -> DecoderLM:
             has_kv=m.kv_from is None, names={role: f"{p}.mix.{role}" for role in "qkvgo"})
         ffn = ffn_norm = None
         if layer.mlp is not None:
-            ffn = SwiGLUFeedForward(f"{p}.mlp", c.hidden_size, layer.mlp.ff, bias=False, alpha=GATE_STEEPNESS,
-                                    limit=layer.mlp.limit, up_shift=UP_SHIFT,
-                                    names={role: f"{p}.mlp.{role}" for role in ("gate", "up", "down")})
+            ffn = GatedFeedForward(f"{p}.mlp", c.hidden_size, layer.mlp.ff, bias=False, alpha=GATE_STEEPNESS,
+                                   limit=layer.mlp.limit, up_shift=UP_SHIFT,
+                                   names={role: f"{p}.mlp.{role}" for role in ("gate", "up", "down")})
             ffn_norm = ConnectedNorm(f"{p}.norm2", c.hidden_size, c.norm_eps, streams, f"{p}.hc2" if connected else None)
         blocks.append(HyperConnectionBlock(
             attention, ffn, ConnectedNorm(f"{p}.norm1", c.hidden_size, c.norm_eps, streams, f"{p}.hc1" if connected else None),

@@ -6,7 +6,7 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
 from .attention import PagedAttention
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
-from .mlp import SwiGLUFeedForward
+from .mlp import GatedFeedForward, SwiGLUFeedForward
 from .norm import RMSNorm
 from .rotary import NoPositionEncoding, RotaryEncoding, YarnRotaryEncoding
 from .streams import ConnectedNorm, HyperConnectionBlock, StreamWrite
@@ -14,5 +14,5 @@ from .streams import ConnectedNorm, HyperConnectionBlock, StreamWrite
 __all__ = ["BLOCKS", "EMBEDDINGS", "HEADS", "Embedding", "Head", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "CacheSpec",
            "FeedForward", "IntoNorm", "LayerBinding", "Mixer", "Norm", "Part", "PositionEncoding", "Registry",
            "Runtime", "StateSpec", "WeightSpec", "PagedAttention", "PreNormBlock", "LMHead",
-           "TokenEmbedding", "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "YarnRotaryEncoding", "ConnectedNorm",
+           "TokenEmbedding", "SwiGLUFeedForward", "GatedFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "YarnRotaryEncoding", "ConnectedNorm",
            "HyperConnectionBlock", "StreamWrite"]

@@ -88,3 +88,7 @@ class SwiGLUFeedForward(FeedForward):
         if into is not None:
             return into.close(hidden, self.down, self.down_bias)
         return ops.linear(hidden, self.down, self.down_bias)
+
+
+# The same part under the name of the general unit: a model whose activation is not SwiGLU builds a `GatedFeedForward`.
+GatedFeedForward = FEED_FORWARDS.register("gated_linear_unit")(SwiGLUFeedForward)
