@@ -15,15 +15,15 @@ extern "C" int ss_attn_simt(const void* q, int64_t q_stride, void* out, int64_t 
                             const int32_t* tile_req, const int32_t* tile_q0, int n_tiles,
                             const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                             int page_size, int64_t num_pages, float scale, int window, int dtype,
-                            const void* gate, int* err, cudaStream_t stream) {
+                            const void* gate, int* err, cudaStream_t stream, float softcap) {
     if (n_tiles <= 0) return 0;
     if (dtype == SS_BF16)
         return launch_attn_simt<bf16, HEAD_DIM>(q, q_stride, out, out_stride, kv, block_tables, max_blocks,
                                                 tile_req, tile_q0, n_tiles, q_start, seq_lens, n_q, n_kv,
-                                                page_size, num_pages, scale, window, gate, err, stream);
+                                                page_size, num_pages, scale, window, gate, err, stream, softcap);
     return launch_attn_simt<float, HEAD_DIM>(q, q_stride, out, out_stride, kv, block_tables, max_blocks,
                                              tile_req, tile_q0, n_tiles, q_start, seq_lens, n_q, n_kv,
-                                             page_size, num_pages, scale, window, gate, err, stream);
+                                             page_size, num_pages, scale, window, gate, err, stream, softcap);
 }
 
 #include "attention_mma.cuh"
@@ -39,7 +39,7 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
                                    const int32_t* tile_req, const int32_t* tile_row0, int n_tiles,
                                    const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                    int page_size, int64_t num_pages, float scale, int window, const void* gate, int* err,
-                                   cudaStream_t stream) {
+                                   cudaStream_t stream, float softcap) {
     if (n_tiles <= 0) return 0;
     constexpr int smem = mma_smem_bytes<HEAD_DIM>();
     static SsPerDevice opted;
@@ -47,7 +47,7 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
     dim3 grid(n_tiles, n_kv);
     ss_launch(attn_prefill_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, tile_req,
-        tile_row0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const bf16*)gate);
+        tile_row0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const bf16*)gate, softcap);
     return SS_LAUNCH_CHECK();
 }
 
@@ -62,7 +62,7 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
                                   const float* inv_freq, int rot_dim, int fused, float* part_o, float* part_lse, int* counters,
-                                  const void* gate, int* err, cudaStream_t stream) {
+                                  const void* gate, int* err, cudaStream_t stream, float softcap) {
     if (n_requests <= 0) return 0;
     const int cluster = n_slices >= 2 && n_slices <= 8;  // the slices are combined through shared memory
     if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
@@ -76,11 +76,11 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
     if (cluster)
         ss_launch_cluster(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, n_slices,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate);
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate, softcap);
     else
         ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate);
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, inv_freq, rot_dim, fused, part_o, part_lse, counters, err, (const bf16*)gate, softcap);
     return SS_LAUNCH_CHECK();
 }
 
@@ -150,7 +150,8 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
                                   const float* inv_freq, int rot_dim, int fused, float* part_o,
-                                  float* part_lse, int* counters, int stages, const void* gate, int* err, cudaStream_t stream) {
+                                  float* part_lse, int* counters, int stages, const void* gate, int* err, cudaStream_t stream,
+                                  float softcap) {
     if (n_requests <= 0) return 0;
     if (page_size % 8 != 0 || 64 % page_size != 0) return -3003;
     // up to 8 slices: one cluster; a multiple of 8 beyond: clusters of 8 whose results meet in scratch memory;
@@ -166,13 +167,13 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     DecodeTmaArgs a;
     a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride; a.kv = (bf16*)kv;
     a.block_tables = block_tables; a.max_blocks = max_blocks; a.q_start = q_start; a.seq_lens = seq_lens;
-    a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.window = window;
+    a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.softcap = softcap; a.window = window;
     a.n_slices = n_slices; a.cluster = cluster; a.inv_freq = inv_freq; a.rot_dim = rot_dim; a.fused = fused;
     a.part_o = part_o; a.part_lse = part_lse; a.counters = counters; a.err = err; a.gate = (const bf16*)gate;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     // the usual decode step (rotation inside, no window, one cluster, a rotary size in steps of 16) has kernels of its own
-    const bool usual = fused && window == 0 && gate == nullptr && cluster == n_slices && cluster > 1 && rot_dim > 0 && rot_dim % 16 == 0;
+    const bool usual = fused && window == 0 && gate == nullptr && softcap <= 0.f && cluster == n_slices && cluster > 1 && rot_dim > 0 && rot_dim % 16 == 0;
     const int smem3 = decode_tma_smem_bytes<HEAD_DIM, 3>(G < 16 ? G : 16, cluster);
     const int smem2 = decode_tma_smem_bytes<HEAD_DIM, 2>(G < 16 ? G : 16, cluster);
     if (stages == 3 && usual) return launch_decode_tma<3, 1>(map_kv, a, grid, cluster, smem3, stream);
@@ -255,7 +256,7 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, (const float*)nullptr, 0, 0, part_o, part_lse, counters, err, (const bf16*)nullptr);
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, (const float*)nullptr, 0, 0, part_o, part_lse, counters, err, (const bf16*)nullptr, 0.f);
     return SS_LAUNCH_CHECK();
 }
 

@@ -53,6 +53,7 @@ struct DecodeTmaArgs {
     int n_q, n_kv, page_size;
     int64_t num_pages;
     float scale;
+    float softcap;  // > 0: scores are squashed to softcap * tanh(score / softcap) before the softmax
     int window, n_slices, cluster;  // cluster: blocks per thread-block cluster along the slices (1: none)
     const float* inv_freq;
     int rot_dim, fused;
@@ -323,7 +324,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks)
                 ldmatrix_x4(qf[ks], Qs + (lane & 15) * KSTR + ks * 16 + ((lane >> 4) << 3));
-            const float scale_log2 = a.scale * 1.4426950408889634f;
+            const float scale_log2 = a.scale * 1.4426950408889634f, cap_log2 = a.softcap * 1.4426950408889634f;
             const int p_lo = (lane >> 2) < heads_here ? pos : -1;
             const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
             // pair (warp / 2) takes the tiles kt_lo + pair, + 2, ...; warp % 2 is the 32-key half.  Tile i lies in
@@ -363,8 +364,8 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                 }
                 if (ok && first_key <= pos) {
                     const bool whole = heads_here == 16 && first_key + 31 <= pos && first_key >= lo;
-                    if (whole) warp_tile<D, 32, false, true>(qf, Ks, Vs, key_off, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
-                    else warp_tile<D, 32, true, true>(qf, Ks, Vs, key_off, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                    if (whole) warp_tile<D, 32, false, true>(qf, Ks, Vs, key_off, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o, cap_log2);
+                    else warp_tile<D, 32, true, true>(qf, Ks, Vs, key_off, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o, cap_log2);
                 }
                 __syncwarp();
                 if (lane == 0) {

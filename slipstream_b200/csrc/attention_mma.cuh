@@ -130,7 +130,7 @@ __device__ __forceinline__ const bf16* tile_at(const bf16* base, int row, int co
 template <int D, int NK, bool MASK, bool SWZ = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const bf16* Ks, const bf16* Vs,
                                           int key_off, int key0_abs, float scale_log2, int pos_lo, int pos_hi,
-                                          int window, float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+                                          int window, float (&m)[2], float (&l)[2], float (&o)[D / 8][4], float cap_log2 = 0.f) {
     constexpr int KSTR = D + 8;
     constexpr int NT = NK / 8;
     const int lane = threadIdx.x & 31;
@@ -162,7 +162,11 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
                 const int pos = (e < 2) ? pos_lo : pos_hi;  // < 0: the row does not exist
                 ok = key <= pos && key >= ((e < 2) ? floor_lo : floor_hi);
             }
-            const float v = ok ? s[n][e] * scale_log2 : -INFINITY;
+            float v = s[n][e] * scale_log2;
+            // a soft cap c on the scaled score: c tanh(score / c), here with both in units of log2(e);
+            // tanh(z) = 1 - 2 / (exp(2 z) + 1), exact at both ends of the range
+            if (cap_log2 > 0.f) v = cap_log2 * (1.0f - __fdividef(2.0f, __expf(2.0f * __fdividef(v, cap_log2)) + 1.0f));
+            if (!ok) v = -INFINITY;
             s[n][e] = v;
             mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -230,7 +234,8 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
                  const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_row0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
-                 int page_size, int64_t num_pages, float scale, int window, int* err, const bf16* __restrict__ gate) {
+                 int page_size, int64_t num_pages, float scale, int window, int* err, const bf16* __restrict__ gate,
+                 float softcap) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int KSTR = D + 8;
@@ -276,7 +281,7 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
 #pragma unroll
     for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     uint32_t qf[D / 16][4];
-    const float scale_log2 = scale * 1.4426950408889634f;
+    const float scale_log2 = scale * 1.4426950408889634f, cap_log2 = softcap * 1.4426950408889634f;
 
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int stage = (kt - kt_lo) & 1;
@@ -305,8 +310,8 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
         const bool whole = warp * 16 + 15 < rows_here && kt * MMA_BN + MMA_BN - 1 <= warp_first_pos &&
                            kt * MMA_BN >= key_floor(warp_last_pos, window);
         if (active) {
-            if (whole) warp_tile<D, MMA_BN, false>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
-            else warp_tile<D, MMA_BN, true>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
+            if (whole) warp_tile<D, MMA_BN, false>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o, cap_log2);
+            else warp_tile<D, MMA_BN, true>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o, cap_log2);
         }
         __syncthreads();
     }
@@ -346,7 +351,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
                 int page_size, int64_t num_pages, float scale, int window, int n_slices, int cluster,
                 const float* __restrict__ inv_freq, int rot_dim, int fused,
                 float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err,
-                const bf16* __restrict__ gate) {
+                const bf16* __restrict__ gate, float softcap) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     // Until pdl_wait() below, only what no kernel of this step writes is touched: the lengths, the block
     // table, and keys and values at positions before the newest token (earlier steps wrote those).  The
@@ -470,7 +475,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             cp_async_commit();
         }
         uint32_t qf[D / 16][4];
-        const float scale_log2 = scale * 1.4426950408889634f;
+        const float scale_log2 = scale * 1.4426950408889634f, cap_log2 = softcap * 1.4426950408889634f;
         const int p_lo = (lane >> 2) < heads_here ? pos : -1;
         const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
         for (int kt = kt_lo; kt <= kt_hi; ++kt) {
@@ -504,8 +509,8 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             if (kt * MMA_BN + warp * 16 <= pos) {
                 const bool whole = heads_here == 16 && kt * MMA_BN + warp * 16 + 15 <= pos &&
                                    kt * MMA_BN + warp * 16 >= key_floor(pos, window);
-                if (whole) warp_tile<D, 16, false>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
-                else warp_tile<D, 16, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                if (whole) warp_tile<D, 16, false>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o, cap_log2);
+                else warp_tile<D, 16, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o, cap_log2);
             }
             __syncthreads();  // the stage may be refilled by the next iteration's prefetch
         }

@@ -35,7 +35,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_q0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                  int n_q, int n_kv, int page_size, int64_t num_pages, float scale, int window,
-                 int* err, const T* __restrict__ gate) {
+                 int* err, const T* __restrict__ gate, float softcap) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int DPL = (D + 31) / 32;
@@ -126,7 +126,8 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
             const int row = w * ATT_RPW + i;
             const int pos = pos0 + row;
             const bool ok = row < rows_here && key <= pos && key >= lowest[i];
-            const float sc = ok ? s[i] * scale : -INFINITY;
+            // softcap > 0: the scaled score is squashed to softcap * tanh(score / softcap) before the softmax
+            const float sc = ok ? (softcap > 0.f ? softcap * tanhf(s[i] * scale / softcap) : s[i] * scale) : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(sc));
             const float pi = (m_new == -INFINITY) ? 0.f : expf(sc - m_new);
             const float alpha = (m[i] == -INFINITY) ? 0.f : expf(m[i] - m_new);
@@ -180,7 +181,7 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
                      const int32_t* block_tables, int max_blocks, const int32_t* tile_req,
                      const int32_t* tile_q0, int n_tiles, const int32_t* q_start,
                      const int32_t* seq_lens, int n_q, int n_kv, int page_size, int64_t num_pages,
-                     float scale, int window, const void* gate, int* err, cudaStream_t stream) {
+                     float scale, int window, const void* gate, int* err, cudaStream_t stream, float softcap = 0.f) {
     static_assert(ATT_RPW == 4, "the kernel packs four rows per warp into a float4");
     constexpr int smem = att_simt_smem_bytes<D>();
     static SsPerDevice opted;
@@ -188,6 +189,6 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
     dim3 grid(n_tiles, n_q);
     ss_launch(attn_simt_kernel<T, D>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv, block_tables, max_blocks, tile_req,
-        tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const T*)gate);
+        tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err, (const T*)gate, softcap);
     return SS_LAUNCH_CHECK();
 }

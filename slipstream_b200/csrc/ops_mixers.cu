@@ -1,0 +1,759 @@
+// Kernels of the parts beside plain attention and the dense feed-forward: a grouped RMS norm on a branch's output,
+// a state-space mixer (short causal convolution and the diagonal recurrence, both with per-request state), routed
+// experts (router, plan, grouped products), weighted query/key norms in front of the rotation with rotated
+// values, the turn back of the heads' outputs, and a soft cap.  Everything the recurrence touches, every norm and
+// every router score is float32; T is the compute type of projections and activations (bfloat16 or float32).
+//
+// Batch layout as everywhere: token-major rows; q_start[r] .. q_start[r + 1] are the rows of request r, seq_lens[r]
+// its cached length after the step.  A request with seq_lens[r] <= 0 is padding of a captured step and is skipped,
+// and so are rows at or beyond q_start[R].
+#include "common.cuh"
+
+// The request whose rows hold `row`: the last r with q_start[r] <= row (requests without rows are passed over);
+// -1 when the row lies beyond the last request.
+__device__ __forceinline__ int request_of_row(const int32_t* __restrict__ q_start, int R, int row) {
+    if (row >= q_start[R]) return -1;
+    int lo = 0, hi = R - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (q_start[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------- grouped RMS norm
+//
+// x_i = sum_{k < terms} in[row][k * hidden + i]  (+ extra[row][i])  (* silu(gate[row][i]))
+// the row in `groups` equal consecutive parts; y_i = x_i / sqrt(mean(part^2) + eps) * weight[i]
+// residual given: residual[row][i] += y_i and out (if given) = residual; else out = y.
+// rows given: source row of output row m is rows[m].
+// A block per output row; a group is summed by GW warps in a fixed order that depends on the sizes only.
+template <typename TI, typename TG, typename TO>
+__global__ void __launch_bounds__(256)
+group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const TO* __restrict__ extra,
+                  const TG* __restrict__ gate, int64_t gate_stride, const float* __restrict__ weight,
+                  float* __restrict__ residual, TO* __restrict__ out, const int32_t* __restrict__ rows, int hidden,
+                  int groups, float eps) {
+    pdl_wait();
+    __shared__ float part[8];
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t row = rows ? rows[m] : m;
+    const int gs = hidden / groups;
+    const int gw = groups >= 8 ? 1 : 8 / groups;  // warps that share a group
+    const int at_once = 8 / gw;                   // groups the block holds at a time
+    const TI* src = in + row * in_stride;
+    for (int g0 = 0; g0 < groups; g0 += at_once) {
+        const int g = g0 + warp / gw, wi = warp % gw;
+        const bool on = g < groups && warp < at_once * gw;
+        float ss = 0.f;
+        if (on) {
+            for (int j = wi * 32 + lane; j < gs; j += gw * 32) {
+                const int i = g * gs + j;
+                float x = to_float(src[i]);
+                for (int k = 1; k < terms; ++k) x += to_float(src[(int64_t)k * hidden + i]);
+                if (extra) x += to_float(extra[row * hidden + i]);
+                if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
+                ss = fmaf(x, x, ss);
+            }
+            ss = warp_sum(ss);
+        }
+        __syncthreads();
+        if (lane == 0) part[warp] = on ? ss : 0.f;
+        __syncthreads();
+        if (on) {
+            float total = 0.f;
+            for (int k = 0; k < gw; ++k) total += part[(warp / gw) * gw + k];
+            const float rstd = 1.0f / sqrtf(total / (float)gs + eps);
+            for (int j = wi * 32 + lane; j < gs; j += gw * 32) {
+                const int i = g * gs + j;
+                float x = to_float(src[i]);
+                for (int k = 1; k < terms; ++k) x += to_float(src[(int64_t)k * hidden + i]);
+                if (extra) x += to_float(extra[row * hidden + i]);
+                if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
+                float y = x * rstd * weight[i];
+                if (residual) {
+                    y += residual[row * hidden + i];
+                    residual[row * hidden + i] = y;
+                }
+                if (out) out[(int64_t)m * hidden + i] = from_float<TO>(y);
+            }
+        }
+    }
+}
+
+// in_type: 0 the compute type, 1 float32.  dtype: the compute type (of out, extra and gate).
+extern "C" int ss_group_norm(const void* in, int in_f32, int64_t in_stride, int terms, const void* extra, const void* gate,
+                             int64_t gate_stride, const float* weight, float* residual, void* out, const int32_t* rows,
+                             int n_out, int hidden, int groups, float eps, int dtype, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (groups < 1 || hidden % groups || terms < 1) return (int)cudaErrorInvalidValue;
+#define GN_GO(TI, T)                                                                                                  \
+    ss_launch(group_norm_kernel<TI, T, T>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms,        \
+              (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps)
+    if (dtype == SS_F32) GN_GO(float, float);
+    else if (in_f32) GN_GO(float, bf16);
+    else GN_GO(bf16, bf16);
+#undef GN_GO
+    return SS_LAUNCH_CHECK();
+}
+
+// The float32 stream rounded to the compute type (what a branch reads).
+__global__ void round_stream_kernel(const float* __restrict__ in, bf16* __restrict__ out, int64_t n) {
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(in[i]);
+}
+
+extern "C" int ss_round_stream(const float* in, void* out, int64_t n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    ss_launch(round_stream_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, in, (bf16*)out, n);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- short causal convolution with state
+//
+// in: channel c of token `row` is proj[row * stride + col0 + c].  out[row][c] = silu(bias[c] + sum_j taps[c][j] *
+// input(t - (T - 1 - j))), where inputs in front of the step's first row come from the request's state
+// [slot][T - 1][C] (float32; index T - 2 is the newest) and inputs in front of the request's first token are the
+// zeros a fresh state holds.  `fused_update`: every request brings one token and the thread that read the state
+// also shifts it; otherwise conv_state_kernel does that in a launch of its own, behind this one.
+#define CONV_MAX_TAPS 8
+#define CONV_ROWS 8
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const float* __restrict__ taps,
+                 const float* __restrict__ bias, float* __restrict__ state, T* __restrict__ out,
+                 const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
+                 const int32_t* __restrict__ slots, int R, int n_rows, int C, int n_taps, int n_slots, int fused_update,
+                 int* err) {
+    pdl_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float w[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < n_taps ? taps[(int64_t)c * n_taps + j] : 0.f;
+    const float b = bias ? bias[c] : 0.f;
+    const int back = n_taps - 1;
+    for (int row = blockIdx.x * CONV_ROWS; row < min(n_rows, (blockIdx.x + 1) * CONV_ROWS); ++row) {
+        const int r = request_of_row(q_start, R, row);
+        if (r < 0) break;
+        if (seq_lens[r] <= 0) continue;
+        const int slot = slots[r];
+        if (slot < 0 || slot >= n_slots) {
+            if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+            continue;
+        }
+        const int i = row - q_start[r];
+        float* st = state + (int64_t)slot * back * C + c;
+        float acc = b;
+        float x[CONV_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j >= n_taps) break;
+            const int src = i - (back - j);
+            x[j] = src >= 0 ? to_float(proj[(int64_t)(row - (back - j)) * stride + col0 + c]) : st[(int64_t)(back + src) * C];
+            acc = fmaf(w[j], x[j], acc);
+        }
+        out[(int64_t)row * C + c] = from_float<T>(silu_exact(acc));
+        if (fused_update) {
+#pragma unroll
+            for (int j = 1; j < CONV_MAX_TAPS; ++j) {
+                if (j >= n_taps) break;
+                st[(int64_t)(j - 1) * C] = x[j];
+            }
+        }
+    }
+}
+
+// The state after the step: the last T - 1 inputs of each request, old ones kept where the step brought fewer.
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_state_kernel(const T* __restrict__ proj, int64_t stride, int col0, float* __restrict__ state,
+                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
+                  const int32_t* __restrict__ slots, int C, int n_taps, int n_slots) {
+    pdl_wait();
+    const int r = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
+    if (c >= C || q_len <= 0 || seq_lens[r] <= 0) return;
+    const int slot = slots[r];
+    if (slot < 0 || slot >= n_slots) return;
+    const int back = n_taps - 1;
+    float* st = state + (int64_t)slot * back * C + c;
+    for (int s = 0; s < back; ++s) {  // ascending: an old value is read before its place is written
+        const int i = q_len - back + s;
+        st[(int64_t)s * C] = i >= 0 ? to_float(proj[(int64_t)(q0 + i) * stride + col0 + c]) : st[(int64_t)(s + q_len) * C];
+    }
+}
+
+extern "C" int ss_conv_silu(const void* proj, int64_t stride, int col0, const float* taps, const float* bias, float* state,
+                            void* out, const int32_t* q_start, const int32_t* seq_lens, const int32_t* slots, int R,
+                            int n_rows, int C, int n_taps, int n_slots, int fused_update, int dtype, int* err,
+                            cudaStream_t stream) {
+    if (n_rows <= 0 || R <= 0) return 0;
+    if (n_taps < 1 || n_taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
+    const dim3 grid((n_rows + CONV_ROWS - 1) / CONV_ROWS, (C + 127) / 128);
+    if (dtype == SS_BF16)
+        ss_launch(conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, stride, col0, taps, bias, state,
+                  (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
+    else
+        ss_launch(conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, stride, col0, taps, bias, state,
+                  (float*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
+    if (!fused_update && n_taps > 1) {
+        const dim3 grid2(R, (C + 127) / 128);
+        if (dtype == SS_BF16)
+            ss_launch(conv_state_kernel<bf16>, grid2, dim3(128), 0, stream, (const bf16*)proj, stride, col0, state, q_start,
+                      seq_lens, slots, C, n_taps, n_slots);
+        else
+            ss_launch(conv_state_kernel<float>, grid2, dim3(128), 0, stream, (const float*)proj, stride, col0, state, q_start,
+                      seq_lens, slots, C, n_taps, n_slots);
+    }
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- the diagonal state-space recurrence
+//
+// Per request, head h (group g = h / (heads / groups)) and token t, with x_t [P], B_t and C_t [N] (the convolution's
+// output: x at column 0, B at heads * P, C behind B), raw step dt_t (a column of the input projection):
+//   dt = softplus(dt_t + dt_bias[h]);  S <- exp(-exp(A_log[h]) dt) S + dt B_t x_t^T;  y_t = S^T C_t + D[h] x_t.
+// S is float32 [N x P] per (slot, head), stored [slot][head][P][N], carried across steps.  A block per (request,
+// head, tile of SCAN_PT columns p); NS = 8 neighbouring lanes share a column, each holding every 8th n in
+// registers; tokens run one after the other, staged SCAN_TB at a time through shared memory.  The order of the
+// arithmetic behind an output does not depend on how the request was cut into steps.
+#define SCAN_NS 8
+#define SCAN_TB 16
+template <typename T, int PER>
+__global__ void __launch_bounds__(1024)
+ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int64_t dt_stride,
+                const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                float* __restrict__ state, float* __restrict__ y, const int32_t* __restrict__ q_start,
+                const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ slots, int heads, int groups, int P,
+                int N, int PT, int n_slots, int* err) {
+    pdl_wait();
+    extern __shared__ float sm[];
+    float* Bs = sm;                      // [TB][N]
+    float* Cs = Bs + SCAN_TB * N;        // [TB][N]
+    float* xs = Cs + SCAN_TB * N;        // [TB][PT]
+    float* dts = xs + SCAN_TB * PT;      // [TB]
+    float* decs = dts + SCAN_TB;         // [TB]
+    const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PT;
+    const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
+    if (q_len <= 0 || seq_lens[r] <= 0) return;
+    const int slot = slots[r];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        return;
+    }
+    const int tid = threadIdx.x, pl = tid / SCAN_NS, ns = tid % SCAN_NS;
+    const int p = p0 + pl;
+    const bool valid = pl < PT && p < P;
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    float* st = state + (((int64_t)slot * heads + h) * P + (valid ? p : 0)) * N;
+    float S[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int n = ns + SCAN_NS * i;
+        S[i] = (valid && n < N) ? st[n] : 0.f;
+    }
+    const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+    for (int t0 = 0; t0 < q_len; t0 += SCAN_TB) {
+        const int nt = min(SCAN_TB, q_len - t0);
+        __syncthreads();
+        for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+            const int tt = idx / N, n = idx - tt * N;
+            const T* row = xbc + (int64_t)(q0 + t0 + tt) * C;
+            Bs[tt * N + n] = to_float(row[inner + g * N + n]);
+            Cs[tt * N + n] = to_float(row[inner + groups * N + g * N + n]);
+        }
+        for (int idx = tid; idx < nt * PT; idx += blockDim.x) {
+            const int tt = idx / PT, j = idx - tt * PT;
+            xs[idx] = (p0 + j < P) ? to_float(xbc[(int64_t)(q0 + t0 + tt) * C + h * P + p0 + j]) : 0.f;
+        }
+        if (tid < nt) {
+            const float z = to_float(dt_raw[(int64_t)(q0 + t0 + tid) * dt_stride + h]) + bias;
+            const float dt = z > 20.f ? z : log1pf(expf(z));
+            dts[tid] = dt;
+            decs[tid] = expf(-rate * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float dec = decs[tt], xv = pl < PT ? xs[tt * PT + pl] : 0.f;
+            const float dx = dts[tt] * xv;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int n = ns + SCAN_NS * i;
+                if (n < N) {
+                    S[i] = fmaf(dec, S[i], dx * Bs[tt * N + n]);
+                    acc = fmaf(S[i], Cs[tt * N + n], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (ns == 0 && valid) y[(int64_t)(q0 + t0 + tt) * inner + h * P + p] = fmaf(skip, xv, acc);
+        }
+    }
+    if (valid) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int n = ns + SCAN_NS * i;
+            if (n < N) st[n] = S[i];
+        }
+    }
+}
+
+extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t dt_stride, const float* dt_bias,
+                           const float* a_log, const float* d_skip, float* state, float* y, const int32_t* q_start,
+                           const int32_t* seq_lens, const int32_t* slots, int R, int heads, int groups, int P, int N,
+                           int n_slots, int dtype, int* err, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (N < 1 || N > 256 || P < 1 || groups < 1 || heads % groups) return (int)cudaErrorInvalidValue;
+    const int PT = min((P + 3) / 4 * 4, 128);
+    const dim3 grid(R, heads, (P + PT - 1) / PT), block(PT * SCAN_NS);
+    const int smem = (2 * SCAN_TB * N + SCAN_TB * PT + 2 * SCAN_TB) * 4;
+    const int per = (N + SCAN_NS - 1) / SCAN_NS;
+#define SCAN_GO(T, PER)                                                                                                 \
+    ss_launch(ssm_scan_kernel<T, PER>, grid, block, smem, stream, (const T*)xbc, C, (const T*)dt_raw, dt_stride, dt_bias,     \
+              a_log, d_skip, state, y, q_start, seq_lens, slots, heads, groups, P, N, PT, n_slots, err)
+#define SCAN_PICK(T)                                                                                                    \
+    if (per <= 8) SCAN_GO(T, 8);                                                                                        \
+    else if (per <= 16) SCAN_GO(T, 16);                                                                                 \
+    else SCAN_GO(T, 32)
+    if (dtype == SS_BF16) { SCAN_PICK(bf16); }
+    else { SCAN_PICK(float); }
+#undef SCAN_PICK
+#undef SCAN_GO
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- router of the routed experts
+//
+// z = W_router x in float32 (x and W in the compute type), the `top` largest z chosen (ties: the lower index);
+// ids[token][k] the chosen expert, w[token][k] = sigmoid(z) of it, or, with `renormalize`, that divided by the
+// sum over the chosen.  A block per token.
+#define ROUTER_MAX_EXPERTS 1024
+template <typename T>
+__global__ void __launch_bounds__(128)
+router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* __restrict__ ids,
+              float* __restrict__ weights, int hidden, int experts, int top, int renormalize) {
+    pdl_wait();
+    extern __shared__ float rsm[];
+    float* xs = rsm;              // [hidden]
+    float* z = rsm + hidden;      // [experts]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < hidden; i += blockDim.x) xs[i] = to_float(x[(int64_t)t * hidden + i]);
+    __syncthreads();
+    for (int e = warp; e < experts; e += 4) {
+        const T* w = w_router + (int64_t)e * hidden;
+        float acc = 0.f;
+        for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(w[i]), xs[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = experts;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; at = e; }  // ascending e: the lower index stays on a tie
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        const float s = 1.0f / (1.0f + expf(-best));
+        total += s;
+        if (lane == 0) {
+            ids[(int64_t)t * top + k] = at < experts ? at : 0;
+            weights[(int64_t)t * top + k] = s;
+            if (at < experts) z[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (renormalize && lane == 0)
+        for (int k = 0; k < top; ++k) weights[(int64_t)t * top + k] /= total;
+}
+
+extern "C" int ss_router(const void* x, const void* w_router, int32_t* ids, float* weights, int n_tokens, int hidden,
+                         int experts, int top, int renormalize, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (experts < 1 || experts > ROUTER_MAX_EXPERTS || top < 1 || top > experts) return (int)cudaErrorInvalidValue;
+    const int smem = (hidden + experts) * 4;
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (dtype == SS_BF16)
+        ss_launch(router_kernel<bf16>, dim3(n_tokens), dim3(128), smem, stream, (const bf16*)x, (const bf16*)w_router, ids,
+                  weights, hidden, experts, top, renormalize);
+    else
+        ss_launch(router_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)x, (const float*)w_router,
+                  ids, weights, hidden, experts, top, renormalize);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- plan of the grouped products
+//
+// A = tokens * top assignments (token t, choice k) -> a = t * top + k.  The plan sorts them by expert:
+// perm[s] = the assignment at sorted place s; an expert's places are consecutive and cut into tiles of `tile`
+// rows: tile_expert[i] (or -1 for a tile that holds nothing), tile_row0[i], tile_rows[i].  The lists have
+// ceil(A / tile) + experts entries, the most any routing needs, so the launch that walks them is the same every
+// step.  One block.  Places within an expert follow the order in which threads arrive; no result depends on it,
+// since every row of a product is computed by itself.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ perm, int32_t* __restrict__ tile_expert,
+                int32_t* __restrict__ tile_row0, int32_t* __restrict__ tile_rows, int A, int experts, int tile,
+                int max_tiles) {
+    pdl_wait();
+    __shared__ int count[ROUTER_MAX_EXPERTS], start[ROUTER_MAX_EXPERTS], first_tile[ROUTER_MAX_EXPERTS + 1];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int a = tid; a < A; a += blockDim.x) atomicAdd(&count[ids[a]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int rows = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = rows;
+            first_tile[e] = tiles;
+            rows += count[e];
+            tiles += (count[e] + tile - 1) / tile;
+        }
+        first_tile[experts] = tiles;
+    }
+    __syncthreads();
+    for (int e = tid; e < experts; e += blockDim.x) {
+        const int n = count[e];
+        for (int i = 0; i * tile < n; ++i) {
+            const int at = first_tile[e] + i;
+            tile_expert[at] = e;
+            tile_row0[at] = start[e] + i * tile;
+            tile_rows[at] = min(tile, n - i * tile);
+        }
+        count[e] = 0;  // from here on: places handed out
+    }
+    for (int i = first_tile[experts] + tid; i < max_tiles; i += blockDim.x) {
+        tile_expert[i] = -1;
+        tile_row0[i] = 0;
+        tile_rows[i] = 0;
+    }
+    __syncthreads();
+    for (int a = tid; a < A; a += blockDim.x) {
+        const int e = ids[a];
+        perm[start[e] + atomicAdd(&count[e], 1)] = a;
+    }
+}
+
+extern "C" int ss_moe_plan(const int32_t* ids, int32_t* perm, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows,
+                           int A, int experts, int tile, int max_tiles, cudaStream_t stream) {
+    if (A <= 0) return 0;
+    if (experts < 1 || experts > ROUTER_MAX_EXPERTS || tile < 1 || max_tiles < (A + tile - 1) / tile + experts)
+        return (int)cudaErrorInvalidValue;
+    ss_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, perm, tile_expert, tile_row0, tile_rows, A, experts, tile,
+              max_tiles);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- grouped products on CUDA cores
+//
+// UP:   hidden[s][n] = silu(g) * u,  g = sum_k a_k Wgu[e][n][k],  u = sum_k a_k Wgu[e][ff + n][k],
+//       a = round_T(w[perm[s]] * x[perm[s] / top])   (the weight is on the expert's input)
+// DOWN: y[perm[s]][n] = sum_k hidden[s][k] Wd[e][n][k]   (float32 out, one row per assignment)
+// for the rows s of the plan's tile blockIdx.x (expert e) and the 64 columns n of blockIdx.y.  float32
+// accumulation in a fixed order.
+#define MG_M 64
+#define MG_N 64
+#define MG_K 16
+template <typename T, bool UP>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, const T* __restrict__ W,
+                const int32_t* __restrict__ perm, const int32_t* __restrict__ tile_expert,
+                const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_rows, T* __restrict__ hidden,
+                float* __restrict__ y, int top, int K, int n_out) {
+    pdl_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = tile_row0[blockIdx.x], rows = tile_rows[blockIdx.x];
+    __shared__ float As[MG_K][MG_M + 4];
+    __shared__ float Ws[UP ? 2 : 1][MG_K][MG_N + 4];
+    __shared__ int src_row[MG_M];
+    __shared__ float src_w[MG_M];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.y * MG_N;
+    if (tid < MG_M) {
+        const int a = tid < rows ? perm[row0 + tid] : -1;
+        src_row[tid] = a;
+        src_w[tid] = (UP && a >= 0) ? weights[a] : 1.f;
+    }
+    __syncthreads();
+    // UP: W is [experts][2 n_out][K]; DOWN: [experts][n_out][K]
+    const T* We = W + (int64_t)e * (UP ? 2 : 1) * n_out * K;
+    float acc[UP ? 2 : 1][4][4];
+#pragma unroll
+    for (int u = 0; u < (UP ? 2 : 1); ++u)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[u][i][j] = 0.f;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    for (int k0 = 0; k0 < K; k0 += MG_K) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int k = k0 + lk + q;
+            float a = 0.f;
+            if (lr < rows && k < K) {
+                if (UP) a = to_float(from_float<T>(src_w[lr] * to_float(x[(int64_t)(src_row[lr] / top) * K + k])));
+                else a = to_float(x[(int64_t)(row0 + lr) * K + k]);
+            }
+            As[lk + q][lr] = a;
+            const int wn = n0 + lr;
+            Ws[0][lk + q][lr] = (wn < n_out && k < K) ? to_float(We[(int64_t)wn * K + k]) : 0.f;
+            if (UP) Ws[1][lk + q][lr] = (wn < n_out && k < K) ? to_float(We[(int64_t)(n_out + wn) * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MG_K; ++kk) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int u = 0; u < (UP ? 2 : 1); ++u) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = Ws[u][kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[u][i][j] = fmaf(a[i], w[j], acc[u][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = ty * 4 + i;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= n_out) continue;
+            if (UP) hidden[(int64_t)(row0 + m) * n_out + n] = from_float<T>(silu_mul<false>(acc[0][i][j], acc[UP ? 1 : 0][i][j]));
+            else y[(int64_t)src_row[m] * n_out + n] = acc[0][i][j];
+        }
+    }
+}
+
+extern "C" int ss_moe_gemm(const void* x, const float* weights, const void* W, const int32_t* perm,
+                           const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* tile_rows, void* hidden,
+                           float* y, int top, int K, int n_out, int max_tiles, int up, int dtype, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    const dim3 grid(max_tiles, (n_out + MG_N - 1) / MG_N);
+#define MG_GO(T, UP)                                                                                                    \
+    ss_launch(moe_gemm_kernel<T, UP>, grid, dim3(256), 0, stream, (const T*)x, weights, (const T*)W, perm, tile_expert,       \
+              tile_row0, tile_rows, (T*)hidden, y, top, K, n_out)
+    if (dtype == SS_BF16) { if (up) MG_GO(bf16, true); else MG_GO(bf16, false); }
+    else { if (up) MG_GO(float, true); else MG_GO(float, false); }
+#undef MG_GO
+    return SS_LAUNCH_CHECK();
+}
+
+// out[t][i] = round_T(sum_k y[t * top + k][i] + shared[t][i]): the chosen experts' outputs in the order of the
+// choices, then the shared expert's.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ shared, T* __restrict__ out,
+                                   int64_t n, int hidden, int top) {
+    pdl_wait();
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int64_t t = idx / hidden;
+    const int i = (int)(idx - t * hidden);
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += y[(t * top + k) * hidden + i];
+    if (shared) v += to_float(shared[idx]);
+    out[idx] = from_float<T>(v);
+}
+
+extern "C" int ss_moe_combine(const float* y, const void* shared, void* out, int n_tokens, int hidden, int top, int dtype,
+                              cudaStream_t stream) {
+    const int64_t n = (int64_t)n_tokens * hidden;
+    if (n <= 0) return 0;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (dtype == SS_BF16)
+        ss_launch(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, y, (const bf16*)shared, (bf16*)out, n, hidden, top);
+    else
+        ss_launch(moe_combine_kernel<float>, grid, dim3(256), 0, stream, y, (const float*)shared, (float*)out, n, hidden, top);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- query/key norm, rotation of q, k and v, page write
+//
+// A token's row holds n_q query heads, n_kv key heads and n_kv value heads of D elements.  Queries and keys: an
+// RMS norm over the head's first norm_dim elements with a weight shared by all heads (q_weight / k_weight, float32
+// [norm_dim]; norm_dim 0: none), then the rotation of the first rot_dim elements by position * inv_freq[i].
+// Values (v_rot_dim > 0): the first v_rot_dim elements rotated by position * v_inv_freq[m].  Pairs are (i, i + dims/2)
+// or, `interleaved`, (2i, 2i + 1).  Queries are written in place, keys and values to their page (in place when the
+// token has no slot).  A warp per head.  kv: [page][2][kv head][offset][D].
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_rope_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* __restrict__ positions,
+                       const int32_t* __restrict__ slots, const float* __restrict__ inv_freq,
+                       const float* __restrict__ v_inv_freq, const float* __restrict__ q_weight,
+                       const float* __restrict__ k_weight, T* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim,
+                       int v_rot_dim, int interleaved, int norm_dim, float eps, int page_size, int64_t pool_slots,
+                       int* err) {
+    pdl_wait();
+    __shared__ float cos_s[128], sin_s[128], vcos_s[128], vsin_s[128];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x) sincosf(__fmul_rn(pos, inv_freq[i]), &sin_s[i], &cos_s[i]);
+    for (int i = threadIdx.x; i < v_rot_dim / 2; i += blockDim.x) sincosf(__fmul_rn(pos, v_inv_freq[i]), &vsin_s[i], &vcos_s[i]);
+    int64_t slot = (slots && kv) ? (int64_t)slots[t] : -1;
+    if (slot >= pool_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        slot = -1;
+    }
+    const int64_t page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? (int)(slot % page_size) : 0;
+    __syncthreads();
+    for (int h = blockIdx.y * n_warps + warp; h < n_q + 2 * n_kv; h += gridDim.y * n_warps) {
+        T* src = rows + (int64_t)t * row_stride + (int64_t)h * D;
+        const bool is_v = h >= n_q + n_kv, is_k = !is_v && h >= n_q;
+        T* dst = src;
+        if (slot >= 0 && is_k) dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+        if (slot >= 0 && is_v) dst = kv + ((((page * 2 + 1) * n_kv + (h - n_q - n_kv)) * page_size + off) * (int64_t)D);
+        constexpr int EPL = 8;  // elements per lane: D <= 256
+        float x[EPL];
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < EPL; ++c) {
+            const int d = lane + 32 * c;
+            x[c] = d < D ? to_float(src[d]) : 0.f;
+            if (d < norm_dim) ss = fmaf(x[c], x[c], ss);
+        }
+        if (!is_v && norm_dim > 0) {
+            const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)norm_dim + eps);
+            const float* w = is_k ? k_weight : q_weight;
+#pragma unroll
+            for (int c = 0; c < EPL; ++c) {
+                const int d = lane + 32 * c;
+                if (d < norm_dim) x[c] = x[c] * rstd * w[d];
+            }
+        }
+        const int dims = is_v ? v_rot_dim : rot_dim, half = dims >> 1;
+        const float* cs = is_v ? vcos_s : cos_s;
+        const float* sn = is_v ? vsin_s : sin_s;
+        // the partner of element d lives in another lane (or another register of this lane): through shared-free
+        // shuffles only when the distance is a multiple of 32, so go through the rounded values in registers
+        float partner[EPL];
+#pragma unroll
+        for (int c = 0; c < EPL; ++c) {
+            const int d = lane + 32 * c;
+            int pd = d;
+            if (d < dims) pd = interleaved ? (d ^ 1) : (d < half ? d + half : d - half);
+            // fetch x of element pd: register pd / 32 of lane pd % 32
+            float v = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < EPL; ++cc) {
+                const float got = __shfl_sync(0xffffffffu, x[cc], pd & 31);
+                if ((pd >> 5) == cc) v = got;
+            }
+            partner[c] = v;
+        }
+#pragma unroll
+        for (int c = 0; c < EPL; ++c) {
+            const int d = lane + 32 * c;
+            if (d >= D) break;
+            float v = x[c];
+            if (d < dims) {
+                const bool first = interleaved ? !(d & 1) : d < half;
+                const int i = interleaved ? (d >> 1) : (first ? d : d - half);
+                // (u, v) -> (u c - v s, v c + u s)
+                v = first ? __fadd_rn(__fmul_rn(x[c], cs[i]), __fmul_rn(-partner[c], sn[i]))
+                          : __fadd_rn(__fmul_rn(x[c], cs[i]), __fmul_rn(partner[c], sn[i]));
+            }
+            dst[d] = from_float<T>(v);
+        }
+    }
+}
+
+extern "C" int ss_norm_rope_cache(void* rows, int64_t row_stride, const int32_t* positions, const int32_t* slots,
+                                  const float* inv_freq, const float* v_inv_freq, const float* q_weight,
+                                  const float* k_weight, void* kv, int n_tokens, int n_q, int n_kv, int D, int rot_dim,
+                                  int v_rot_dim, int interleaved, int norm_dim, float eps, int page_size,
+                                  int64_t num_pages, int dtype, int* err, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D < 2 || D > 256 || rot_dim < 0 || rot_dim > D || rot_dim % 2 || v_rot_dim < 0 || v_rot_dim > D || v_rot_dim % 2 ||
+        norm_dim < 0 || norm_dim > D || (rot_dim > 0 && !inv_freq) || (v_rot_dim > 0 && !v_inv_freq) ||
+        (norm_dim > 0 && (!q_weight || (n_kv > 0 && !k_weight))))
+        return (int)cudaErrorInvalidValue;
+    const int heads = n_q + 2 * n_kv;
+    const int warps = heads >= 8 ? 8 : (heads >= 4 ? 4 : 2);
+    const dim3 grid(n_tokens, (heads + warps - 1) / warps);
+    const int64_t pool = num_pages * page_size;
+    if (dtype == SS_BF16)
+        ss_launch(norm_rope_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)rows, row_stride, positions, slots,
+                  inv_freq, v_inv_freq, q_weight, k_weight, (bf16*)kv, n_q, n_kv, D, rot_dim, v_rot_dim, interleaved,
+                  norm_dim, eps, page_size, pool, err);
+    else
+        ss_launch(norm_rope_cache_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)rows, row_stride, positions,
+                  slots, inv_freq, v_inv_freq, q_weight, k_weight, (float*)kv, n_q, n_kv, D, rot_dim, v_rot_dim, interleaved,
+                  norm_dim, eps, page_size, pool, err);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- turning the heads' outputs back
+//
+// x: [tokens][heads * D] in place; the first `dims` elements of every head are rotated by sign * position *
+// inv_freq[m], pairs as above.  A thread per pair.
+template <typename T>
+__global__ void turn_heads_kernel(T* __restrict__ x, const int32_t* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int64_t n_pairs, int heads, int D, int dims,
+                                  int interleaved, float sign) {
+    pdl_wait();
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_pairs) return;
+    const int half = dims >> 1;
+    const int m = (int)(idx % half);
+    const int64_t th = idx / half;  // token * heads + head
+    const int64_t t = th / heads;
+    float sn, cs;
+    sincosf(__fmul_rn((float)positions[t], inv_freq[m]), &sn, &cs);
+    sn *= sign;
+    T* head = x + th * D;
+    const int i0 = interleaved ? 2 * m : m, i1 = interleaved ? 2 * m + 1 : m + half;
+    const float u = to_float(head[i0]), v = to_float(head[i1]);
+    head[i0] = from_float<T>(__fadd_rn(__fmul_rn(u, cs), __fmul_rn(-v, sn)));
+    head[i1] = from_float<T>(__fadd_rn(__fmul_rn(v, cs), __fmul_rn(u, sn)));
+}
+
+extern "C" int ss_turn_heads(void* x, const int32_t* positions, const float* inv_freq, int n_tokens, int heads, int D,
+                             int dims, int interleaved, float sign, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || dims <= 0) return 0;
+    if (dims % 2 || dims > D) return (int)cudaErrorInvalidValue;
+    const int64_t n_pairs = (int64_t)n_tokens * heads * (dims / 2);
+    const dim3 grid((unsigned)((n_pairs + 255) / 256));
+    if (dtype == SS_BF16)
+        ss_launch(turn_heads_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)x, positions, inv_freq, n_pairs, heads, D, dims,
+                  interleaved, sign);
+    else
+        ss_launch(turn_heads_kernel<float>, grid, dim3(256), 0, stream, (float*)x, positions, inv_freq, n_pairs, heads, D,
+                  dims, interleaved, sign);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- soft cap:  x <- cap * tanh(x / cap)
+__global__ void soft_cap_kernel(float* __restrict__ x, int64_t n, float cap) {
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int ss_soft_cap(float* x, int64_t n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    ss_launch(soft_cap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+    return SS_LAUNCH_CHECK();
+}

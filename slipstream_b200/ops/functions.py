@@ -59,24 +59,41 @@ _OPS_SIGNATURES = {
                            c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
     "ss_glu_limited": [c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
     "ss_sigmoid_gate": [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p],
+    "ss_group_norm": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "ss_round_stream": [c_void_p, c_void_p, c_int64, c_void_p],
+    "ss_conv_silu": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_ssm_scan": [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_router": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_int, c_int, c_int, c_void_p],
+    "ss_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_void_p,
+                           c_void_p],
+    "ss_turn_heads": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "ss_soft_cap": [c_void_p, c_int64, c_float, c_void_p],
 }
 
 _ATTN_SIGNATURES = {
     "ss_attn_simt": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                      c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
-                     c_int, c_int, c_void_p, c_void_p, c_void_p],
+                     c_int, c_int, c_void_p, c_void_p, c_void_p, c_float],
     "ss_attn_prefill_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
-                            c_int, c_void_p, c_void_p, c_void_p],
+                            c_int, c_void_p, c_void_p, c_void_p, c_float],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                             c_void_p, c_void_p],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float],
 }
 
 _GEMM_SIGNATURES = {
@@ -120,7 +137,7 @@ def ops_library() -> ctypes.CDLL:
     lib = _state.get("ops")
     if lib is None:
         require_cuda()
-        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "sampling.cu"])
+        lib = load_library("slipstream_ops", ["ops.cu", "ops_streams.cu", "ops_mixers.cu", "sampling.cu"])
         _declare(lib, _OPS_SIGNATURES)
         _state["ops"] = lib
     return lib  # type: ignore[return-value]
@@ -511,8 +528,10 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
                          block_tables: torch.Tensor, tile_req: torch.Tensor, tile_q0: torch.Tensor,
                          q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
                          head_dim: int, scale: float, window: int = 0, chunk: int = 0,
-                         gate: torch.Tensor | None = None) -> None:
+                         gate: torch.Tensor | None = None, softcap: float = 0.0) -> None:
     """Causal grouped-query attention of the step's query rows over the pages (``window`` / ``chunk``: `key_span`).
+    ``softcap`` c > 0 (in every attention entry point but the tcgen05 one): a scaled score s enters the softmax as
+    ``c * tanh(s / c)``.
     ``gate`` (in every attention entry point): a view of the same rows as ``q`` ([N, n_q * D], rows ``q_stride``
     apart); the output is multiplied by its sigmoid as it is written.
 
@@ -529,14 +548,16 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
                             block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                             tile_q0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                             n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
-                            _code(q.dtype), _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream()),
+                            _code(q.dtype), _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream(),
+                            float(softcap or 0.0)),
            "paged_attention_simt")
 
 
 def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                             block_tables: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor,
                             q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                            scale: float, window: int = 0, chunk: int = 0, gate: torch.Tensor | None = None) -> None:
+                            scale: float, window: int = 0, chunk: int = 0, gate: torch.Tensor | None = None,
+                            softcap: float = 0.0) -> None:
     """bfloat16 tensor-core attention for prompt portions and mixed batches.  A tile is 64 consecutive
     rows of one request, a row being a (query token, head of the kv group) pair in token-major order:
     ``tile_req`` / ``tile_row0`` list (request index, first row)."""
@@ -552,7 +573,8 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
                                    block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                                    tile_row0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                                    n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), key_span(window, chunk),
-                                   _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream()),
+                                   _gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream(),
+                                   float(softcap or 0.0)),
            "paged_attention_prefill")
 
 
@@ -641,7 +663,8 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
                            rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None,
-                           stages: int = 2, chunk: int = 0, gate: torch.Tensor | None = None) -> None:
+                           stages: int = 2, chunk: int = 0, gate: torch.Tensor | None = None,
+                           softcap: float = 0.0) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
     through shared memory; with more, the partial results (of every cluster of 8 in the TMA-fed kernel when the
@@ -694,7 +717,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
             int(rope is not None), _ptr(part_o), _ptr(part_lse), _ptr(counters))
     if gate is not None and rope is not None:
         raise KernelError("a gated layer does not rotate inside the decode kernel")
-    tail = (_gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream())
+    tail = (_gate_ptr(gate, q, q_stride), error_word(q.device).data_ptr(), _stream(), float(softcap or 0.0))
     if tma:
         _check(lib.ss_attn_decode_tma(*args, int(stages), *tail), "paged_attention_decode")
     else:
@@ -753,7 +776,7 @@ def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
                     ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                     rope: tuple[torch.Tensor | None, int] | None = None, chunk: int = 0,
-                    gate: torch.Tensor | None = None) -> None:
+                    gate: torch.Tensor | None = None, softcap: float = 0.0) -> None:
     """Attention of the step's rows over the pages, choosing the kernel for the batch.
 
     ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
@@ -772,7 +795,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     if qkv.dtype == torch.float32:
         tile_req, tile_q0 = ctx.query_tiles(16)
         paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
-                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate)
+                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate, softcap)
         return
     group = n_q // n_kv
     if ctx.is_decode_only:
@@ -785,9 +808,9 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
-                               stages=DECODE_RING_STAGES, chunk=chunk, gate=gate)
+                               stages=DECODE_RING_STAGES, chunk=chunk, gate=gate, softcap=softcap)
         return
-    if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
+    if not softcap and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
         key = ("prefill_key_parts", 128 // group, n_kv)
         parts = ctx.extras.get(key)
@@ -801,7 +824,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         return
     tile_req, tile_row0 = ctx.query_tiles(64, group)
     paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
-                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate)
+                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window, chunk, gate, softcap)
 
 
 # --------------------------------------------------------------------------- sampling
@@ -1336,6 +1359,251 @@ def gate_up_glu(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: tor
     return glu_limited(linear(x, weight, bias), block, alpha, limit, shift)
 
 
+# --------------------------------------------------------------------------- grouped norm, state-space mixer, routed experts
+
+def group_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype, *,
+               residual: torch.Tensor | None = None, rows: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+               terms: int = 1, extra: torch.Tensor | None = None, want_out: bool = True) -> torch.Tensor | None:
+    """RMS norm in ``groups`` equal consecutive parts of the last axis, each part over its own root mean square
+    (``v / sqrt(mean(v^2) + eps)``), times ``weight`` (float32 [hidden]); float32 arithmetic, one rounding.
+
+    ``x`` [N, hidden] in ``out_dtype`` or float32.  ``terms`` > 1: ``x`` is [N, terms, hidden] (float32) and the
+    terms are summed first; ``extra`` [N, hidden] (``out_dtype``) is added to that sum.  ``gate`` (a view [N, hidden]
+    with unit inner stride, ``out_dtype``): the input is multiplied by ``silu(gate)`` before the norm.
+    ``residual`` (float32 [N, hidden]): the result is ADDED to it in place, and what is returned is the new
+    residual rounded to ``out_dtype`` (nothing with ``want_out`` False).  ``rows`` (int32 [M]): only those rows
+    of ``x`` are normed and returned."""
+    hidden = weight.numel()
+    _need(weight, torch.float32, "norm weight")
+    if x.dtype not in (out_dtype, torch.float32) or not x.is_cuda or not x.is_contiguous():
+        raise KernelError("group_norm takes a contiguous CUDA tensor in the compute dtype or float32")
+    if terms > 1 and (x.dim() != 3 or x.shape[1] != terms or x.dtype != torch.float32):
+        raise KernelError("with terms, x must be float32 [N, terms, hidden]")
+    if x.shape[-1] != hidden or groups < 1 or hidden % groups:
+        raise KernelError(f"group_norm: {hidden} features do not split into {groups} groups, or x is of another width")
+    n = x.shape[0]
+    n_out = n if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        if residual is not None:
+            raise KernelError("a selection of rows is not added to the stream")
+    if residual is not None:
+        _need(residual, torch.float32, "residual")
+        if tuple(residual.shape) != (n, hidden):
+            raise KernelError("residual does not match x")
+    if extra is not None:
+        _need(extra, out_dtype, "extra")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != out_dtype or gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (n, hidden):
+            raise KernelError("the gate must be [N, hidden] in the compute dtype with unit inner stride")
+        gate_stride = gate.stride(0)
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if want_out else None
+    _check(ops_library().ss_group_norm(x.data_ptr(), int(x.dtype == torch.float32), terms * hidden, int(terms), _ptr(extra),
+                                       _ptr(gate), gate_stride, weight.data_ptr(), _ptr(residual), _ptr(out), _ptr(rows),
+                                       n_out, hidden, int(groups), float(eps), _code(out_dtype), _stream()), "group_norm")
+    return out
+
+
+def round_stream(residual: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """The float32 stream as a branch reads it: itself in float32, rounded once in bfloat16."""
+    _need(residual, torch.float32, "residual")
+    if out_dtype == torch.float32:
+        return residual
+    out = torch.empty(residual.shape, dtype=torch.bfloat16, device=residual.device)
+    _check(ops_library().ss_round_stream(residual.data_ptr(), out.data_ptr(), residual.numel(), _stream()), "round_stream")
+    return out
+
+
+def conv_silu(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, bias: torch.Tensor | None,
+              state: torch.Tensor, ctx) -> torch.Tensor:
+    """``silu`` of a causal convolution per channel over each request's tokens.  Channel c of a token is
+    ``proj[row, col0 + c]``; ``taps`` float32 [channels, T] (the last column multiplies the current token);
+    ``state`` float32 [slots, T - 1, channels] holds each request's last T - 1 inputs (zeros for a request that
+    starts), is read for the tokens in front of the step and left holding the step's last inputs.  Returns
+    [N, channels] in the dtype of ``proj``."""
+    _need(proj, None, "projection")
+    _need(taps, torch.float32, "taps")
+    _need(state, torch.float32, "convolution state")
+    n_taps = taps.shape[1]
+    if bias is not None:
+        _need(bias, torch.float32, "convolution bias")
+    if tuple(taps.shape) != (channels, n_taps) or tuple(state.shape[1:]) != (max(n_taps - 1, 0), channels):
+        raise KernelError("taps must be [channels, T] and the state [slots, T - 1, channels]")
+    if col0 < 0 or col0 + channels > proj.shape[1] or n_taps > 8:
+        raise KernelError("the convolution's channels lie outside the projection, or it has more than 8 taps")
+    n = proj.shape[0]
+    out = torch.empty((n, channels), dtype=proj.dtype, device=proj.device)
+    _check(ops_library().ss_conv_silu(proj.data_ptr(), proj.stride(0), int(col0), taps.data_ptr(), _ptr(bias),
+                                      state.data_ptr(), out.data_ptr(), ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(),
+                                      ctx.state_slots.data_ptr(), ctx.num_requests, n, channels, n_taps, state.shape[0],
+                                      int(ctx.is_decode_only), _code(proj.dtype), error_word(proj.device).data_ptr(),
+                                      _stream()), "conv_silu")
+    if not ctx.is_decode_only and n_taps > 1:
+        _launches[0] += 1  # the state's update is a launch of its own
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, ctx, heads: int, groups: int, head_dim: int, state_dim: int) -> torch.Tensor:
+    """The diagonal state-space recurrence over each request's tokens, continued from and left in ``state``
+    (float32 [slots, heads, head_dim, state_dim]).  ``xbc`` [N, heads * head_dim + 2 * groups * state_dim] holds x, then
+    B, then C; ``dt`` [N, heads] is a view of the raw step sizes (unit inner stride).  Per head h (group
+    ``h // (heads / groups)``): ``dt' = softplus(dt + dt_bias[h])``, ``S <- exp(-exp(a_log[h]) dt') S + dt' B x^T``,
+    ``y = S^T C + d_skip[h] x``.  Returns y float32 [N, heads * head_dim]."""
+    _need(xbc, None, "x, B and C")
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip), ("state", state)):
+        _need(t, torch.float32, name)
+    n = xbc.shape[0]
+    inner = heads * head_dim
+    if xbc.shape[1] != inner + 2 * groups * state_dim or dt.dtype != xbc.dtype or dt.stride(1) != 1 or tuple(dt.shape) != (n, heads):
+        raise KernelError("ssm_scan: xbc or dt has the wrong shape")
+    if tuple(state.shape[1:]) != (heads, head_dim, state_dim) or state_dim > 256:
+        raise KernelError("ssm_scan: the state must be [slots, heads, head_dim, state_dim] with state_dim <= 256")
+    y = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
+    _check(ops_library().ss_ssm_scan(xbc.data_ptr(), xbc.shape[1], dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(),
+                                     a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), y.data_ptr(),
+                                     ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(),
+                                     ctx.num_requests, heads, groups, head_dim, state_dim, state.shape[0], _code(xbc.dtype),
+                                     error_word(xbc.device).data_ptr(), _stream()), "ssm_scan")
+    return y
+
+
+def router(x: torch.Tensor, weight: torch.Tensor, top: int, renormalize: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """Sigmoid router: logits ``x @ weight.T`` in float32, the ``top`` largest per token chosen (the lower index on a
+    tie).  Returns (int32 [N, top] experts, float32 [N, top] their scores ``sigmoid(logit)``, divided by their sum with
+    ``renormalize``)."""
+    _need(x, None, "x")
+    _need(weight, x.dtype, "router weight")
+    n, hidden = x.shape
+    experts = weight.shape[0]
+    if weight.shape[1] != hidden or not 1 <= top <= experts or experts > 1024 or (hidden + experts) * 4 > 48 * 1024:
+        raise KernelError("router: sizes out of range")
+    ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    scores = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    _check(ops_library().ss_router(x.data_ptr(), weight.data_ptr(), ids.data_ptr(), scores.data_ptr(), n, hidden, experts,
+                                   int(top), int(renormalize), _code(x.dtype), _stream()), "router")
+    return ids, scores
+
+
+MOE_TILE = 64  # rows of one expert that a block of the grouped products takes
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
+                ) -> torch.Tensor:
+    """The chosen experts of every token: ``y[t, k] = W_down[e] (silu(W_gate[e] a) * (W_up[e] a))`` with
+    ``e = ids[t, k]`` and ``a = scores[t, k] * x[t]`` (the score multiplies the expert's INPUT), rounded to the
+    compute dtype.  ``gate_up`` [experts, 2 ff, hidden] (gate rows, then up rows), ``down`` [experts, hidden, ff].
+    Returns float32 [N, top, hidden].  Three launches whatever the routing: the plan (assignments sorted by expert and
+    cut into tiles), the up product with the activation, the down product."""
+    n, hidden = x.shape
+    experts, two_ff, _ = gate_up.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    _need(x, None, "x")
+    _need(gate_up, x.dtype, "gate_up")
+    _need(down, x.dtype, "down")
+    _need(ids, torch.int32, "ids")
+    _need(scores, torch.float32, "scores")
+    if tuple(down.shape) != (experts, hidden, ff) or gate_up.shape[2] != hidden:
+        raise KernelError("moe_experts: weights of the wrong shape")
+    a = n * top
+    max_tiles = (a + MOE_TILE - 1) // MOE_TILE + experts
+    plan = torch.empty(a + 3 * max_tiles, dtype=torch.int32, device=x.device)
+    perm, tile_expert = plan[:a], plan[a: a + max_tiles]
+    tile_row0, tile_rows = plan[a + max_tiles: a + 2 * max_tiles], plan[a + 2 * max_tiles:]
+    lib = ops_library()
+    _check(lib.ss_moe_plan(ids.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
+                           tile_rows.data_ptr(), a, experts, MOE_TILE, max_tiles, _stream()), "moe_plan")
+    hidden_act = torch.empty((a, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((n, top, hidden), dtype=torch.float32, device=x.device)
+    _check(lib.ss_moe_gemm(x.data_ptr(), scores.data_ptr(), gate_up.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(),
+                           tile_row0.data_ptr(), tile_rows.data_ptr(), hidden_act.data_ptr(), None, top, hidden, ff,
+                           max_tiles, 1, _code(x.dtype), _stream()), "moe_up")
+    _check(lib.ss_moe_gemm(hidden_act.data_ptr(), None, down.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(),
+                           tile_row0.data_ptr(), tile_rows.data_ptr(), None, y.data_ptr(), top, ff, hidden,
+                           max_tiles, 0, _code(x.dtype), _stream()), "moe_down")
+    return y
+
+
+def moe_combine(y: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
+    """``sum_k y[t, k] + shared[t]`` rounded to ``out_dtype``: the chosen experts' outputs in the order of the choices,
+    then the shared expert's."""
+    _need(y, torch.float32, "expert outputs")
+    n, top, hidden = y.shape
+    if shared is not None:
+        _need(shared, out_dtype, "shared expert output")
+    out = torch.empty((n, hidden), dtype=out_dtype, device=y.device)
+    _check(ops_library().ss_moe_combine(y.data_ptr(), _ptr(shared), out.data_ptr(), n, hidden, top, _code(out_dtype),
+                                        _stream()), "moe_combine")
+    return out
+
+
+def norm_rope_cache(rows: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor | None, kv: torch.Tensor | None,
+                    n_q: int, n_kv: int, head_dim: int, *, inv_freq: torch.Tensor | None = None, rotary_dim: int = 0,
+                    value_inv_freq: torch.Tensor | None = None, value_rotary_dim: int = 0, interleaved: bool = False,
+                    q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None, norm_dim: int = 0,
+                    eps: float = 0.0, write_cache: bool = True) -> None:
+    """For a layer's projected heads (``rows`` [N, >= (n_q + 2 n_kv) * head_dim]: queries, keys, values): an RMS norm
+    of every query and key head over its first ``norm_dim`` elements with a weight shared by the heads (float32
+    [norm_dim]) BEFORE the rotation; the rotation of the first ``rotary_dim`` elements of queries and keys by
+    position * ``inv_freq``; the rotation of the first ``value_rotary_dim`` elements of every value head by position *
+    ``value_inv_freq``; pairs (i, i + dims / 2) or, ``interleaved``, (2i, 2i + 1).  Queries change in place; keys
+    and values go to their pages ``kv`` [pages, 2, n_kv, page_size, head_dim] at ``slots``."""
+    _need(rows, None, "projected rows")
+    _need(positions, torch.int32, "positions")
+    n, width = rows.shape
+    if width < (n_q + 2 * n_kv) * head_dim:
+        raise KernelError("the projected rows are narrower than their heads")
+    for t, dims, what in ((inv_freq, rotary_dim, "inv_freq"), (value_inv_freq, value_rotary_dim, "value_inv_freq")):
+        if dims:
+            _need(t, torch.float32, what)
+            if dims % 2 or dims > head_dim or t.numel() != dims // 2:
+                raise KernelError(f"{what} must hold dims / 2 values, dims even and at most head_dim")
+    if norm_dim:
+        _need(q_weight, torch.float32, "q norm weight")
+        if n_kv:
+            _need(k_weight, torch.float32, "k norm weight")
+        if q_weight.numel() != norm_dim or (n_kv and k_weight.numel() != norm_dim) or norm_dim > head_dim:
+            raise KernelError("query/key norm weights must hold norm_dim values")
+    write = bool(write_cache and n_kv and kv is not None and slots is not None)
+    pages, page_size = 0, 1
+    if write:
+        _need(kv, rows.dtype, "kv pages")
+        _need(slots, torch.int32, "slots")
+        if kv.dim() != 5 or kv.shape[1] != 2 or kv.shape[2] != n_kv or kv.shape[4] != head_dim:
+            raise KernelError(f"kv pages have shape {tuple(kv.shape)}, expected [pages, 2, {n_kv}, page, {head_dim}]")
+        pages, page_size = kv.shape[0], kv.shape[3]
+    _check(ops_library().ss_norm_rope_cache(rows.data_ptr(), width, positions.data_ptr(), _ptr(slots) if write else None,
+                                            _ptr(inv_freq) if rotary_dim else None,
+                                            _ptr(value_inv_freq) if value_rotary_dim else None,
+                                            _ptr(q_weight) if norm_dim else None, _ptr(k_weight) if norm_dim and n_kv else None,
+                                            _ptr(kv) if write else None, n, n_q, n_kv, head_dim, int(rotary_dim),
+                                            int(value_rotary_dim), int(interleaved), int(norm_dim), float(eps), page_size,
+                                            pages, _code(rows.dtype), error_word(rows.device).data_ptr(), _stream()),
+           "norm_rope_cache")
+
+
+def turn_heads(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, heads: int, head_dim: int, dims: int,
+               interleaved: bool = False, sign: float = -1.0) -> None:
+    """Rotate the first ``dims`` elements of every head of ``x`` [N, heads * head_dim] in place by
+    ``sign * position * inv_freq`` (pairs as in `norm_rope_cache`): with ``sign`` -1 the turn back of heads' outputs
+    that were summed over rotated values."""
+    _need(x, None, "heads")
+    _need(positions, torch.int32, "positions")
+    _need(inv_freq, torch.float32, "inv_freq")
+    if x.shape[1] != heads * head_dim or dims % 2 or dims > head_dim or inv_freq.numel() != dims // 2:
+        raise KernelError("turn_heads: sizes do not match")
+    _check(ops_library().ss_turn_heads(x.data_ptr(), positions.data_ptr(), inv_freq.data_ptr(), x.shape[0], heads, head_dim,
+                                       int(dims), int(interleaved), float(sign), _code(x.dtype), _stream()), "turn_heads")
+
+
+def soft_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x <- cap * tanh(x / cap)`` in place (float32)."""
+    _need(x, torch.float32, "x")
+    _check(ops_library().ss_soft_cap(x.data_ptr(), x.numel(), float(cap), _stream()), "soft_cap")
+    return x
+
+
 def set_programmatic_launch(enabled: bool) -> None:
     """Turn programmatic dependent launch of this package's kernels on or off (on by default)."""
     libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if isinstance(key, str) and key.startswith("attn")]
@@ -1348,4 +1616,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_norm", "linear_hc_rmsnorm", "rope_norm_cache", "glu_limited", "gate_up_glu", "sigmoid_gate", "key_span", "rope_and_cache", "swiglu",
            "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
-           "attention_library"]
+           "attention_library", "group_norm", "round_stream", "conv_silu", "ssm_scan", "router", "moe_experts", "moe_combine",
+           "norm_rope_cache", "turn_heads", "soft_cap"]

@@ -4,10 +4,12 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    Embedding, FeedForward, Head, IntoNorm, LayerBinding, Mixer, Norm, Part, PositionEncoding, Registry, Runtime,
                    StateSpec, WeightSpec)
 from .attention import PagedAttention
-from .block import PreNormBlock
+from .block import BranchNormBlock, PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .mlp import GatedFeedForward, SwiGLUFeedForward
-from .norm import RMSNorm
+from .experts import RoutedExperts
+from .norm import GroupRMSNorm, RMSNorm, StreamRounding
+from .state_space import StateSpaceMixer
 from .rotary import NoPositionEncoding, RotaryEncoding, YarnRotaryEncoding
 from .streams import ConnectedNorm, HyperConnectionBlock, StreamWrite
 
@@ -15,4 +17,5 @@ __all__ = ["BLOCKS", "EMBEDDINGS", "HEADS", "Embedding", "Head", "FEED_FORWARDS"
            "FeedForward", "IntoNorm", "LayerBinding", "Mixer", "Norm", "Part", "PositionEncoding", "Registry",
            "Runtime", "StateSpec", "WeightSpec", "PagedAttention", "PreNormBlock", "LMHead",
            "TokenEmbedding", "SwiGLUFeedForward", "GatedFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "YarnRotaryEncoding", "ConnectedNorm",
-           "HyperConnectionBlock", "StreamWrite"]
+           "HyperConnectionBlock", "StreamWrite", "BranchNormBlock", "GroupRMSNorm", "StreamRounding", "RoutedExperts",
+           "StateSpaceMixer"]

@@ -15,8 +15,13 @@ request's first token.  ``value_dim``: values (and the heads' outputs) of anothe
 (``x / sqrt(mean(x^2) + eps)``, no weight); the pages hold the keys in that form.  ``gate``: the concatenated
 heads are multiplied by ``sigmoid(W_g x)`` before the output projection (``W_g`` reads the same input as q/k/v).
 ``has_kv`` False: the layer has no key/value projections and attends over pages that another layer wrote (the
-model's order names it).  ``names``: the checkpoint's tensor names by role (q, k, v, o, g, q_bias, k_bias,
-v_bias, o_bias).
+model's order names it).  ``qk_norm_eps``: BEFORE the rotation every query and key head passes an RMS norm over its
+elements with a weight of the head's size that all heads share (tensors ``q_norm`` / ``k_norm``).  ``rotate_values``:
+the value of position j is rotated by j over all its elements, with the pairing of the position encoding and the
+frequencies ``theta^(-2m / value_dim)``, and cached so; a head's output at position i (the weighted sum of such
+values) is turned back by -i before any gate, so that what is summed depends on i - j only.  ``softcap`` c: a scaled
+score s enters the softmax as ``c tanh(s / c)``.  ``names``: the checkpoint's tensor names by role (q, k, v, o, g,
+q_bias, k_bias, v_bias, o_bias, q_norm, k_norm).
 
 Heads of a size the kernels do not take (they take multiples of 16), or values of another size than keys, are
 padded with zeros where the weights are bound: q/k/v/g rows and o columns of the padding are zero, so the
@@ -42,7 +47,8 @@ class PagedAttention(Mixer):
                  position_encoding: PositionEncoding, qkv_bias: bool = True, out_bias: bool = False,
                  window: int | None = None, scale: float | None = None, page_size: int | None = None, *,
                  chunk: int | None = None, value_dim: int | None = None, unit_norm_eps: float | None = None,
-                 gate: bool = False, has_kv: bool = True, names: dict[str, str] | None = None) -> None:
+                 gate: bool = False, has_kv: bool = True, names: dict[str, str] | None = None,
+                 qk_norm_eps: float | None = None, rotate_values: bool = False, softcap: float | None = None) -> None:
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})")
         value_dim = head_dim if value_dim is None else int(value_dim)
@@ -69,13 +75,23 @@ class PagedAttention(Mixer):
         self.chunk = chunk
         self.unit_norm_eps = None if unit_norm_eps is None else float(unit_norm_eps)
         self.gate = bool(gate)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.rotate_values = bool(rotate_values)
+        self.softcap = float(softcap) if softcap else None
+        if self.rotate_values and (value_dim % 2 or getattr(position_encoding, "theta", None) is None):
+            raise ValueError("rotated values need an even value size and a rotary position encoding")
+        if self.rotate_values and gate:
+            raise ValueError("a gate on rotated values is not built")
+        if self.qk_norm_eps is not None and unit_norm_eps is not None:
+            raise ValueError("a layer norms its heads before the rotation or after it, not both")
         self.has_kv = bool(has_kv)
         self.page_size = page_size  # tokens per cache page this layer wants; None: the engine's default
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         n = name
         self.names = {"q": f"{n}.q_proj.weight", "k": f"{n}.k_proj.weight", "v": f"{n}.v_proj.weight",
                       "o": f"{n}.o_proj.weight", "g": f"{n}.g_proj.weight", "q_bias": f"{n}.q_proj.bias",
-                      "k_bias": f"{n}.k_proj.bias", "v_bias": f"{n}.v_proj.bias", "o_bias": f"{n}.o_proj.bias"}
+                      "k_bias": f"{n}.k_proj.bias", "v_bias": f"{n}.v_proj.bias", "o_bias": f"{n}.o_proj.bias",
+                      "q_norm": f"{n}.q_norm.weight", "k_norm": f"{n}.k_norm.weight"}
         self.names.update(names or {})
 
     @property
@@ -84,6 +100,7 @@ class PagedAttention(Mixer):
         rotation (half-split pairs, unscaled sines, no unit norm, no gate, keys and values of its own)."""
         rotary_plain = getattr(self.position_encoding, "plain", True)
         return (rotary_plain and self.unit_norm_eps is None and not self.gate and self.has_kv
+                and self.qk_norm_eps is None and not self.rotate_values and self.softcap is None
                 and self.key_dim == self.value_dim == self.head_dim)
 
     def weight_specs(self) -> list[WeightSpec]:
@@ -100,6 +117,10 @@ class PagedAttention(Mixer):
                           WeightSpec(names["v_bias"], (self.num_kv_heads * dv,), kind="vector")]
         if self.out_bias:
             specs.append(WeightSpec(names["o_bias"], (h,), kind="vector"))
+        if self.qk_norm_eps is not None:
+            specs.append(WeightSpec(names["q_norm"], (d,), kind="vector", init=("one_plus_normal", 0.1)))
+            if self.has_kv:
+                specs.append(WeightSpec(names["k_norm"], (d,), kind="vector", init=("one_plus_normal", 0.1)))
         return specs
 
     def cache_spec(self) -> CacheSpec:
@@ -135,6 +156,14 @@ class PagedAttention(Mixer):
         self.o_weight = o
         self.o_b = weights[names["o_bias"]].to(runtime.dtype) if self.out_bias else None
         self.position_encoding.bind(weights, runtime)
+        self.q_norm_weight = self.k_norm_weight = self.value_inv_freq = None
+        if self.qk_norm_eps is not None:
+            self.q_norm_weight = weights[names["q_norm"]].to(torch.float32).contiguous()
+            if self.has_kv:
+                self.k_norm_weight = weights[names["k_norm"]].to(torch.float32).contiguous()
+        if self.rotate_values:  # formed in double precision, rounded once
+            pairs = torch.arange(0, self.value_dim, 2, dtype=torch.float64)
+            self.value_inv_freq = (float(self.position_encoding.theta) ** (-pairs / self.value_dim)).to(torch.float32).to(runtime.device)
         ops.attention_library(self.head_dim)  # compile now, not inside the first step
 
     # ------------------------------------------------------------------ decode steps replayed from a graph
@@ -146,8 +175,8 @@ class PagedAttention(Mixer):
         if plan is None or plan.is_decode_only:
             return bool(bf16 and ops.is_long_context(longest))
         group = self.num_heads // self.num_kv_heads
-        if not bf16 or not ops.tcgen05_attention_fits(self.head_dim, self.num_heads, self.num_kv_heads, self.page_size or 16,
-                                          self.window or 0):
+        if not bf16 or self.softcap or not ops.tcgen05_attention_fits(self.head_dim, self.num_heads, self.num_kv_heads,
+                                                                      self.page_size or 16, self.window or 0):
             return None
         return int(ops.prefill_key_parts(plan.q_lens, plan.seq_lens, 128 // group, self.num_kv_heads,
                                          ops.sm_count(self.runtime.device)))
@@ -189,7 +218,22 @@ class PagedAttention(Mixer):
         # a decode step's attention kernel rotates and writes the newest key and value itself
         fused = (plain_projection and self.plain and layer.writes_cache
                  and ops.fuses_rope(qkv, ctx, self.head_dim, self.num_heads, self.num_kv_heads, layer.kv.shape[3]))
-        if not self.plain:
+        early_norm = self.qk_norm_eps is not None or self.rotate_values
+        if early_norm:
+            if getattr(self.position_encoding, "mscale", 1.0) != 1.0:
+                raise ValueError(f"{self.name}: scaled sines are not built for layers that norm before the rotation")
+            if self.has_kv != layer.writes_cache:
+                raise ValueError(f"{self.name}: a layer with keys and values of its own writes its pages, one without "
+                                 "reads another layer's")
+            ops.norm_rope_cache(qkv, ctx.positions, meta.slot_mapping, layer.kv, self.num_heads,
+                                self.num_kv_heads if self.has_kv else 0, self.head_dim, inv_freq=inv_freq,
+                                rotary_dim=rotary_dim, value_inv_freq=self.value_inv_freq,
+                                value_rotary_dim=self.value_dim if self.rotate_values else 0,
+                                interleaved=getattr(self.position_encoding, "interleaved", False),
+                                q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
+                                norm_dim=self.key_dim if self.qk_norm_eps is not None else 0, eps=self.qk_norm_eps or 0.0,
+                                write_cache=layer.writes_cache)
+        elif not self.plain:
             if self.has_kv != layer.writes_cache:
                 raise ValueError(f"{self.name}: a layer with keys and values of its own writes its pages, one without "
                                  "reads another layer's")
@@ -207,7 +251,10 @@ class PagedAttention(Mixer):
         ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.scale, self.window or 0,
                             rope=(inv_freq, rotary_dim) if fused else None, chunk=self.chunk or 0,
-                            gate=qkv[:, qkv.shape[1] - out.shape[1]:] if self.gate else None)
+                            gate=qkv[:, qkv.shape[1] - out.shape[1]:] if self.gate else None, softcap=self.softcap or 0.0)
+        if self.rotate_values:
+            ops.turn_heads(out, ctx.positions, self.value_inv_freq, self.num_heads, self.head_dim, self.value_dim,
+                           interleaved=getattr(self.position_encoding, "interleaved", False), sign=-1.0)
         if into is not None:
             return into.close(out, self.o_weight, self.o_b)
         return ops.linear(out, self.o_weight, self.o_b)

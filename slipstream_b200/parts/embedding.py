@@ -44,7 +44,9 @@ class LMHead(Head):
     takes_pending_norm = True  # ``forward`` hands x to ``ops.linear`` as it is
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None,
-                 tensor: str | None = None) -> None:
+                 tensor: str | None = None, softcap: float | None = None) -> None:
+        """``softcap`` c: the logits leave as ``c * tanh(logits / c)``."""
+        self.softcap = float(softcap) if softcap else None
         self.name = name
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
@@ -62,4 +64,5 @@ class LMHead(Head):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, None, out_dtype=torch.float32)
+        logits = ops.linear(x, self.weight, None, out_dtype=torch.float32)
+        return ops.soft_cap(logits, self.softcap) if self.softcap else logits
