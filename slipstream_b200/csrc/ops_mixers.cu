@@ -331,9 +331,9 @@ extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t d
 
 // ---------------------------------------------------------------- router of the routed experts
 //
-// z = W_router x in float32 (x and W in the compute type), the `top` largest z chosen (ties: the lower index);
-// ids[token][k] the chosen expert, w[token][k] = sigmoid(z) of it, or, with `renormalize`, that divided by the
-// sum over the chosen.  A block per token.
+// z = W_router x in float32 (x and W in the compute type), scores s = sigmoid(z) in float32, the `top` largest
+// scores chosen (ties, which saturated scores make real: the lower index); ids[token][k] the chosen expert,
+// w[token][k] = its score, or, with `renormalize`, that divided by the sum over the chosen.  A block per token.
 #define ROUTER_MAX_EXPERTS 1024
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -351,7 +351,7 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* 
         float acc = 0.f;
         for (int i = lane; i < hidden; i += 32) acc = fmaf(to_float(w[i]), xs[i], acc);
         acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+        if (lane == 0) z[e] = 1.0f / (1.0f + expf(-acc));  // the score; the choice below is among scores
     }
     __syncthreads();
     if (warp != 0) return;
@@ -369,7 +369,7 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ w_router, int32_t* 
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
         }
-        const float s = 1.0f / (1.0f + expf(-best));
+        const float s = best;
         total += s;
         if (lane == 0) {
             ids[(int64_t)t * top + k] = at < experts ? at : 0;
