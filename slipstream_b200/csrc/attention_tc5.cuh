@@ -148,6 +148,7 @@ struct Args {
     float scale;
     int* err;
     int span;  // what a query sees besides the causal rule (common.cuh: key_floor); 0: every earlier key
+    float softcap;  // > 0: a scaled score s enters the softmax as softcap * tanh(s / softcap)
 };
 
 template <int D>
@@ -371,7 +372,8 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
         const int pos = pos0 + tok;
         const int lowest = key_floor(pos, a.span);  // the first key this row sees
-        const float scale_log2 = a.scale * 1.4426950408889634f;
+        const float cap_log2 = a.softcap * 1.4426950408889634f;
+        const float scale_log2 = cap_log2 > 0.f ? 1.0f : a.scale * 1.4426950408889634f;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -384,6 +386,16 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tmem_ld32(tmem + lane_base + st * FA_BN, sr[0]);
             tmem_ld32(tmem + lane_base + st * FA_BN + 32, sr[1]);
             tmem_ld_wait();
+            if (cap_log2 > 0.f) {
+                // capped scores, in units of log2(e): c tanh(s / c) with tanh(z) = 1 - 2 / (exp(2 z) + 1); from here
+                // on the registers hold scaled scores and the scale below is 1
+                const float pre = 2.0f * __fdividef(a.scale * 1.4426950408889634f, cap_log2);
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const float t = __expf(__uint_as_float(sr[c >> 5][c & 31]) * pre);
+                    sr[c >> 5][c & 31] = __float_as_uint(cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f)));
+                }
+            }
             // raw scores; the scale is folded into the exponent below.  Four running maxima keep the chain short.
             const int key0 = (t_lo + j) * FA_BN;
             if (key0 + FA_BN - 1 > pos) {  // the diagonal tile: keys after the row's own position are masked

@@ -561,6 +561,197 @@ extern "C" int ss_moe_gemm(const void* x, const float* weights, const void* W, c
     return SS_LAUNCH_CHECK();
 }
 
+// ---------------------------------------------------------------- grouped products on the tensor cores (bfloat16)
+//
+// The same two products with mma.sync.m16n8k16 tiles fed by ldmatrix from a three-stage cp.async ring.  The rows of an
+// expert are contiguous in sorted order, so the activations are first gathered into that order (and, for the up
+// product, multiplied by the router's score and rounded) by moe_gather_kernel; a block then takes one tile of BM
+// sorted rows (the plan's tile size) and 64 output columns: for UP the 64 gate rows and the 64 matching up rows of
+// the expert's stacked weight, whose accumulators meet in the epilogue as silu(g) * u.  K and n_out are multiples of 8.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool on) {
+    const int bytes = on ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t r[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// sorted[s][k] = round(w[perm[s]] * x[perm[s] / top][k]) for the `total` assignments (8 elements a thread).
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, const float* __restrict__ weights,
+                                  const int32_t* __restrict__ perm, bf16* __restrict__ sorted, int total, int top, int K) {
+    pdl_wait();
+    const int chunks = K / 8;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)total * chunks) return;
+    const int s = (int)(idx / chunks), c = (int)(idx - (int64_t)s * chunks);
+    const int a = perm[s];
+    const float w = weights[a];
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + (int64_t)(a / top) * K + c * 8);
+    const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&in[e]);
+        const __nv_bfloat162 r = __floats2bfloat162_rn(w * __low2float(v), w * __high2float(v));
+        out[e] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(sorted + (int64_t)s * K + c * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+#define MM_BK 32
+#define MM_STR (MM_BK + 8)
+#define MM_STAGES 3
+template <int BM, bool UP>
+constexpr int moe_mma_smem() { return MM_STAGES * (BM + (UP ? 128 : 64)) * MM_STR * 2; }
+
+template <int BM, int WARPS_M, bool UP>
+__global__ void __launch_bounds__(256)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, const int32_t* __restrict__ perm,
+                    const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_row0,
+                    const int32_t* __restrict__ tile_rows, bf16* __restrict__ hidden, float* __restrict__ y, int K,
+                    int n_out) {
+    constexpr int WARPS_N = 8 / WARPS_M, TM = BM / WARPS_M, TN = 64 / WARPS_N, MT = TM / 16, NT = TN / 8;
+    constexpr int NB = UP ? 128 : 64, U = UP ? 2 : 1;
+    static_assert(TM % 16 == 0 && TN % 16 == 0, "a warp's tile is whole m16 x n16 pieces");
+    pdl_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int row0 = tile_row0[blockIdx.x], rows = tile_rows[blockIdx.x], n0 = blockIdx.y * 64;
+    extern __shared__ __align__(16) unsigned char mm_raw[];
+    bf16* As = reinterpret_cast<bf16*>(mm_raw);                 // [stage][BM][MM_STR]
+    bf16* Bs = As + MM_STAGES * BM * MM_STR;                    // [stage][NB][MM_STR]
+    const bf16* We = W + (int64_t)e * U * n_out * K;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp / WARPS_N, wn = warp % WARPS_N;
+
+    auto load_stage = [&](int stage, int k0) {
+        bf16* as = As + stage * BM * MM_STR;
+        bf16* bs = Bs + stage * NB * MM_STR;
+        for (int c = tid; c < BM * 4; c += 256) {
+            const int r = c >> 2, kc = (c & 3) * 8;
+            const bool on = r < rows && k0 + kc < K;
+            cp_async_16(as + r * MM_STR + kc, A + (on ? (int64_t)(row0 + r) * K + k0 + kc : 0), on);
+        }
+        for (int c = tid; c < NB * 4; c += 256) {
+            const int r = c >> 2, kc = (c & 3) * 8;
+            const int n = n0 + (r & 63);
+            const bool on = n < n_out && k0 + kc < K;
+            const int64_t wrow = (UP && r >= 64) ? n_out + n : n;  // gate rows, then the matching up rows
+            cp_async_16(bs + r * MM_STR + kc, We + (on ? wrow * K + k0 + kc : 0), on);
+        }
+    };
+
+    float acc[U][MT][NT][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) acc[u][i][j][0] = acc[u][i][j][1] = acc[u][i][j][2] = acc[u][i][j][3] = 0.f;
+
+    const int k_steps = (K + MM_BK - 1) / MM_BK;
+#pragma unroll
+    for (int s = 0; s < MM_STAGES - 1; ++s) {
+        if (s < k_steps) load_stage(s, s * MM_BK);
+        cp_async_commit();
+    }
+    for (int ks = 0; ks < k_steps; ++ks) {
+        cp_async_wait<MM_STAGES - 2>();
+        __syncthreads();
+        if (ks + MM_STAGES - 1 < k_steps) load_stage((ks + MM_STAGES - 1) % MM_STAGES, (ks + MM_STAGES - 1) * MM_BK);
+        cp_async_commit();
+        const bf16* as = As + (ks % MM_STAGES) * BM * MM_STR;
+        const bf16* bs = Bs + (ks % MM_STAGES) * NB * MM_STR;
+#pragma unroll
+        for (int kk = 0; kk < MM_BK; kk += 16) {
+            uint32_t af[MT][4];
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+                ldsm_x4(af[i], as + (wm * TM + i * 16 + (lane & 15)) * MM_STR + kk + ((lane >> 4) << 3));
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    uint32_t b[4];
+                    const int brow = u * 64 + wn * TN + j * 8 + (lane & 7) + ((lane >> 4) << 3);
+                    ldsm_x4(b, bs + brow * MM_STR + kk + (((lane >> 3) & 1) << 3));
+#pragma unroll
+                    for (int i = 0; i < MT; ++i) {
+                        mma_16816(acc[u][i][j], af[i], b[0], b[1]);
+                        mma_16816(acc[u][i][j + 1], af[i], b[2], b[3]);
+                    }
+                }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = wm * TM + i * 16 + (lane >> 2) + half * 8;
+            if (m >= rows) continue;
+            const int64_t out_row = UP ? (int64_t)(row0 + m) : (int64_t)perm[row0 + m];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int n = n0 + wn * TN + j * 8 + ((lane & 3) << 1);
+                if (n >= n_out) continue;  // n_out is even: a pair is in or out together
+                if (UP) {
+                    const float h0 = silu_mul<true>(acc[0][i][j][half * 2], acc[U - 1][i][j][half * 2]);
+                    const float h1 = silu_mul<true>(acc[0][i][j][half * 2 + 1], acc[U - 1][i][j][half * 2 + 1]);
+                    *reinterpret_cast<__nv_bfloat162*>(hidden + out_row * n_out + n) = __floats2bfloat162_rn(h0, h1);
+                } else {
+                    *reinterpret_cast<float2*>(y + out_row * n_out + n) = make_float2(acc[0][i][j][half * 2], acc[0][i][j][half * 2 + 1]);
+                }
+            }
+        }
+}
+
+template <int BM, int WARPS_M, bool UP>
+static int launch_moe_mma(const void* A, const void* W, const int32_t* perm, const int32_t* tile_expert,
+                          const int32_t* tile_row0, const int32_t* tile_rows, void* hidden, float* y, int K, int n_out,
+                          int max_tiles, cudaStream_t stream) {
+    constexpr int smem = moe_mma_smem<BM, UP>();
+    static SsPerDevice opted;
+    if (int rc = ss_opt_in_smem(moe_gemm_mma_kernel<BM, WARPS_M, UP>, smem, opted)) return rc;
+    ss_launch(moe_gemm_mma_kernel<BM, WARPS_M, UP>, dim3(max_tiles, (n_out + 63) / 64), dim3(256), smem, stream,
+              (const bf16*)A, (const bf16*)W, perm, tile_expert, tile_row0, tile_rows, (bf16*)hidden, y, K, n_out);
+    return SS_LAUNCH_CHECK();
+}
+
+// tile: the plan's tile size, 128 or 32.  up: A is the gathered activations, the output the hidden rows; else A the
+// hidden rows and the output one float32 row per assignment.
+extern "C" int ss_moe_gemm_mma(const void* A, const void* W, const int32_t* perm, const int32_t* tile_expert,
+                               const int32_t* tile_row0, const int32_t* tile_rows, void* hidden, float* y, int K, int n_out,
+                               int max_tiles, int tile, int up, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    if (K % 8 || n_out % 8 || (tile != 128 && tile != 32) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+        return (int)cudaErrorInvalidValue;
+    if (tile == 128)
+        return up ? launch_moe_mma<128, 4, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream)
+                  : launch_moe_mma<128, 4, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream);
+    return up ? launch_moe_mma<32, 2, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream)
+              : launch_moe_mma<32, 2, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream);
+}
+
+extern "C" int ss_moe_gather(const void* x, const float* weights, const int32_t* perm, void* sorted, int total, int top,
+                             int K, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (K % 8) return (int)cudaErrorInvalidValue;
+    const int64_t n = (int64_t)total * (K / 8);
+    ss_launch(moe_gather_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const bf16*)x, weights, perm,
+              (bf16*)sorted, total, top, K);
+    return SS_LAUNCH_CHECK();
+}
+
 // out[t][i] = round_T(sum_k y[t * top + k][i] + shared[t][i]): the chosen experts' outputs in the order of the
 // choices, then the shared expert's.
 template <typename T>

@@ -70,6 +70,9 @@ _OPS_SIGNATURES = {
     "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ss_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_int, c_int, c_void_p],
+    "ss_moe_gemm_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_int, c_int, c_void_p],
+    "ss_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "ss_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ss_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_void_p,
@@ -87,7 +90,7 @@ _ATTN_SIGNATURES = {
                             c_int, c_void_p, c_void_p, c_void_p, c_float],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                            c_void_p, c_void_p],
+                            c_void_p, c_void_p, c_float],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float],
@@ -579,16 +582,24 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
 
 
 def tcgen05_attention_fits(head_dim: int, n_q: int, n_kv: int, page_size: int, window: int) -> bool:
-    """Whether the tcgen05 prefill attention kernel takes this layer: head size 64 or 128, no sliding window (a
-    chunked mask it takes: `paged_attention_prefill_tcgen05`'s ``chunk``), pages of 8, 16, 32 or 64 tokens, at most 128
-    query heads per kv head."""
+    """Whether the TMA-fed decode attention kernel takes this layer (``window`` 0), or the tcgen05 prefill kernel
+    without a sliding window: head size 64 or 128, pages of 8, 16, 32 or 64 tokens, at most 128 query heads per kv
+    head.  (The prefill kernel also takes windows, chunked masks and soft caps: `tcgen05_prefill_fits`.)"""
     return (head_dim in (64, 128) and not window and page_size in (8, 16, 32, 64) and n_q // n_kv <= 128)
+
+
+def tcgen05_prefill_fits(head_dim: int, n_q: int, n_kv: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill attention kernel takes this layer, whatever its mask (a sliding window, a chunked
+    mask or none: the kernel starts at the first key tile a query tile can see and masks by row) and with or without
+    a soft cap on the scores."""
+    return tcgen05_attention_fits(head_dim, n_q, n_kv, page_size, 0)
 
 
 def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                                     block_tables: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
                                     q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
-                                    head_dim: int, scale: float, key_parts: int = 1, chunk: int = 0) -> None:
+                                    head_dim: int, scale: float, key_parts: int = 1, chunk: int = 0, window: int = 0,
+                                    softcap: float = 0.0) -> None:
     """bfloat16 causal attention for prompt portions and mixed batches on the tcgen05 tensor cores (Q, K, V
     tiles by TMA, S and O in tensor memory).  A tile is ``128 // (n_q // n_kv)`` consecutive query tokens of
     one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows); blocks
@@ -611,12 +622,13 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
                                    block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                                    tile_tok0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
                                    n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(key_parts),
-                                   key_span(0, chunk), error_word(q.device).data_ptr(), _stream()),
+                                   key_span(window, chunk), error_word(q.device).data_ptr(), _stream(),
+                                   float(softcap or 0.0)),
            "paged_attention_prefill_tcgen05")
 
 
 def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int, n_kv: int,
-                      sms: int | None = None) -> int:
+                      sms: int | None = None, span: int = 0) -> int:
     """Into how many parts the tcgen05 prefill kernel should cut the keys of its query tiles.  A block walks its
     key tiles one after the other, about a microsecond each, so a step with few query tiles lasts as long as its
     longest one while most SMs idle: a portion of 64 tokens behind 4,096 cached ones is 16 blocks of 64 key
@@ -631,6 +643,8 @@ def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int
     counts = (q_lens + tile_tokens - 1) // tile_tokens
     blocks = int(counts.sum()) * n_kv
     longest = int(seq_lens.max() - 1) // 64 + 1  # key tiles of the last query tile of the longest request
+    if span > 0:  # under a window or a chunked mask a query tile sees no more than this many
+        longest = min(longest, (span + tile_tokens) // 64 + 2)
     sms = sms or sm_count()
     parts = 1
     while parts < 8 and blocks * parts * 2 <= 2 * sms and longest >= 16 * parts:
@@ -810,15 +824,15 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
                                stages=DECODE_RING_STAGES, chunk=chunk, gate=gate, softcap=softcap)
         return
-    if not softcap and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
+    if tcgen05_prefill_fits(head_dim, n_q, n_kv, kv.shape[3]):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
-        key = ("prefill_key_parts", 128 // group, n_kv)
+        key = ("prefill_key_parts", 128 // group, n_kv, window or chunk)
         parts = ctx.extras.get(key)
-        if parts is None:  # the same for every layer of the step
+        if parts is None:  # the same for every layer of the step that sees as far
             parts = ctx.extras[key] = prefill_key_parts(ctx.q_lens_host, ctx.seq_lens_host, 128 // group, n_kv,
-                                                        sm_count(qkv.device))
+                                                        sm_count(qkv.device), window or chunk)
         paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
-                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts, chunk)
+                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts, chunk, window, softcap)
         if gate is not None:
             sigmoid_gate(out, gate)
         return
@@ -1494,8 +1508,10 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_u
     """The chosen experts of every token: ``y[t, k] = W_down[e] (silu(W_gate[e] a) * (W_up[e] a))`` with
     ``e = ids[t, k]`` and ``a = scores[t, k] * x[t]`` (the score multiplies the expert's INPUT), rounded to the
     compute dtype.  ``gate_up`` [experts, 2 ff, hidden] (gate rows, then up rows), ``down`` [experts, hidden, ff].
-    Returns float32 [N, top, hidden].  Three launches whatever the routing: the plan (assignments sorted by expert and
-    cut into tiles), the up product with the activation, the down product."""
+    Returns float32 [N, top, hidden].  The same launches whatever the routing: the plan (assignments sorted by expert
+    and cut into tiles), the up product with the activation, the down product.  bfloat16 with sizes in steps of 8
+    runs the products on the tensor cores (tiles of 128 sorted rows when experts get many rows each, of 32 otherwise),
+    behind a gather of the scaled activations into sorted order; everything else runs them on CUDA cores."""
     n, hidden = x.shape
     experts, two_ff, _ = gate_up.shape
     ff, top = two_ff // 2, ids.shape[1]
@@ -1507,15 +1523,27 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_u
     if tuple(down.shape) != (experts, hidden, ff) or gate_up.shape[2] != hidden:
         raise KernelError("moe_experts: weights of the wrong shape")
     a = n * top
-    max_tiles = (a + MOE_TILE - 1) // MOE_TILE + experts
+    tensor_cores = x.dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0
+    tile = MOE_TILE if not tensor_cores else (128 if a >= 96 * experts else 32)
+    max_tiles = (a + tile - 1) // tile + experts
     plan = torch.empty(a + 3 * max_tiles, dtype=torch.int32, device=x.device)
     perm, tile_expert = plan[:a], plan[a: a + max_tiles]
     tile_row0, tile_rows = plan[a + max_tiles: a + 2 * max_tiles], plan[a + 2 * max_tiles:]
     lib = ops_library()
     _check(lib.ss_moe_plan(ids.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
-                           tile_rows.data_ptr(), a, experts, MOE_TILE, max_tiles, _stream()), "moe_plan")
+                           tile_rows.data_ptr(), a, experts, tile, max_tiles, _stream()), "moe_plan")
     hidden_act = torch.empty((a, ff), dtype=x.dtype, device=x.device)
     y = torch.empty((n, top, hidden), dtype=torch.float32, device=x.device)
+    if tensor_cores:
+        lists = (perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr())
+        gathered = torch.empty((a, hidden), dtype=x.dtype, device=x.device)
+        _check(lib.ss_moe_gather(x.data_ptr(), scores.data_ptr(), perm.data_ptr(), gathered.data_ptr(), a, top, hidden,
+                                 _stream()), "moe_gather")
+        _check(lib.ss_moe_gemm_mma(gathered.data_ptr(), gate_up.data_ptr(), *lists, hidden_act.data_ptr(), None, hidden, ff,
+                                   max_tiles, tile, 1, _stream()), "moe_up")
+        _check(lib.ss_moe_gemm_mma(hidden_act.data_ptr(), down.data_ptr(), *lists, None, y.data_ptr(), ff, hidden,
+                                   max_tiles, tile, 0, _stream()), "moe_down")
+        return y
     _check(lib.ss_moe_gemm(x.data_ptr(), scores.data_ptr(), gate_up.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(),
                            tile_row0.data_ptr(), tile_rows.data_ptr(), hidden_act.data_ptr(), None, top, hidden, ff,
                            max_tiles, 1, _code(x.dtype), _stream()), "moe_up")
@@ -1615,6 +1643,6 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "hc_norm", "linear_hc_rmsnorm", "rope_norm_cache", "glu_limited", "gate_up_glu", "sigmoid_gate", "key_span", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "tcgen05_prefill_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library", "group_norm", "round_stream", "conv_silu", "ssm_scan", "router", "moe_experts", "moe_combine",
            "norm_rope_cache", "turn_heads", "soft_cap"]

@@ -175,20 +175,21 @@ class PagedAttention(Mixer):
         if plan is None or plan.is_decode_only:
             return bool(bf16 and ops.is_long_context(longest))
         group = self.num_heads // self.num_kv_heads
-        if not bf16 or self.softcap or not ops.tcgen05_attention_fits(self.head_dim, self.num_heads, self.num_kv_heads,
-                                                                      self.page_size or 16, self.window or 0):
+        if not bf16 or not ops.tcgen05_prefill_fits(self.head_dim, self.num_heads, self.num_kv_heads, self.page_size or 16):
             return None
         return int(ops.prefill_key_parts(plan.q_lens, plan.seq_lens, 128 // group, self.num_kv_heads,
-                                         ops.sm_count(self.runtime.device)))
+                                         ops.sm_count(self.runtime.device), self.window or self.chunk or 0))
 
     def capture_group(self) -> object:
-        return "paged_attention"
+        # layers that see equally far answer `capture_variant` alike
+        return ("paged_attention", self.window or self.chunk or 0)
 
     def prepare_capture(self, ctx, variant: object, max_model_len: int) -> None:
         if not ctx.is_decode_only:
             # a captured step with prompt portions: the number of key parts is the variant's (the choice follows the
             # lengths of the step, which a replay does not know on the host)
-            ctx.extras[("prefill_key_parts", 128 // (self.num_heads // self.num_kv_heads), self.num_kv_heads)] = int(variant or 1)
+            ctx.extras[("prefill_key_parts", 128 // (self.num_heads // self.num_kv_heads), self.num_kv_heads,
+                        self.window or self.chunk or 0)] = int(variant or 1)
             return
         # the number of slices must not follow the lengths of the step that happens to be captured
         ctx.extras["static_max_seq_len"] = max_model_len

@@ -370,7 +370,8 @@ def test_recurrence_against_the_literal_loop_however_it_is_cut(heads, groups, p,
 @pytest.mark.gpu
 @pytest.mark.parametrize("experts, top, hidden, ff, dtype", [(5, 2, 64, 24, torch.float32), (12, 1, 96, 40, torch.float32),
                                                            (8, 3, 128, 64, torch.bfloat16), (3, 3, 40, 100, torch.float32),
-                                                           (70, 4, 72, 16, torch.bfloat16)])
+                                                           (70, 4, 72, 16, torch.bfloat16), (3, 2, 64, 72, torch.bfloat16),
+                                                           (5, 2, 36, 20, torch.bfloat16)])
 def test_router_and_grouped_products(experts, top, hidden, ff, dtype):
     from slipstream_b200 import ops
     g = torch.Generator().manual_seed(experts * 10 + top)
