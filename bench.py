@@ -15,6 +15,10 @@ beside this file when present.  One GPU only: for --gpus above 1 it says so and 
 heads, clamped gated feed-forward) beside the Qwen2.5 decoder at equal layer sizes: prefill and decode throughput
 at three sizes, and every kernel the design adds beside the like kernel of the Qwen2.5 path with both rooflines.
 
+``--compare sarudra`` does the same for the Sarudra decoder (state-space layers with per-request state and windowed
+attention layers with query/key norms, rotated values and soft-capped scores in turn, routed experts beside a shared
+one, grouped norms on the branches' outputs).
+
 ``--only decode|prefill`` runs one part and prints a short line (profiling, and measurements beside the
 headline): ``--only decode --batch 1 --prompt-len 32000 --context-len 32768`` is a decode step behind a long
 context, ``--only prefill --chunk 512 --prefix 8192 --context-len 32768`` a prompt portion behind cached tokens.
@@ -28,6 +32,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import types
 import threading
 import time
 
@@ -378,6 +383,76 @@ def compare_configs(z: dict, chunk: int, streams: int, share_kv: bool) -> tuple[
     return qwen, fokedra
 
 
+def measure_model(config: dict, args, pk: dict, rng) -> dict:
+    """Prefill of one prompt of ``args.chunk`` tokens in one step (median of five, each by itself) and decode of
+    ``args.batch`` requests behind ``args.prompt_len`` cached tokens, for the model ``config`` with random weights."""
+    import torch
+
+    from slipstream_b200 import ops
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+
+    batch, ctx_tokens, T, page = args.batch, args.prompt_len, args.chunk, 16
+    folder = tempfile.mkdtemp(prefix="bench_compare_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(config, f)
+    pages = (batch * (ctx_tokens + args.steps + args.warmup + 16) + 2 * T) // page + 64
+    runner = ModelRunner(folder, dtype="bfloat16", page_size=page, num_pages=pages, max_num_seqs=max(batch, 4),
+                         max_model_len=8192, load_format="random", use_cuda_graphs=not args.no_graphs)
+    vocab = runner.config.vocab_size
+    # prefill: one prompt of T tokens in one step, as the captured graph a running engine replays; median of five
+    times = []
+    for w in range(getattr(runner, "mixed_graph_after", 0) + 2 + 5):
+        toks = rng.integers(0, vocab, T).tolist()
+        torch.cuda.synchronize()
+        time.sleep(0.2)  # a step by itself, as the burst peak it is compared with
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(f"p{w}", toks, [T - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.release(f"p{w}")
+        times.append(start.elapsed_time(stop))
+    prefill_ms = sorted(times[-5:])[2]
+    print(f"[bench]   prefill {prefill_ms:.3f} ms", file=sys.stderr, flush=True)
+    # decode: `batch` requests behind `ctx_tokens` cached tokens each
+    ids = [f"d{i}" for i in range(batch)]
+    per_step = max(1, 4096 // ctx_tokens)
+    for i in range(0, batch, per_step):
+        runner.step([StepEntry(r, rng.integers(0, vocab, ctx_tokens).tolist(), []) for r in ids[i:i + per_step]])
+    feeds = rng.integers(0, vocab, (args.steps + args.warmup, batch)).tolist()
+    for w in range(args.warmup):
+        runner.step([StepEntry(r, [feeds[w][j]], [0]) for j, r in enumerate(ids)])
+    torch.cuda.synchronize()
+    launches0 = ops.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for s in range(args.steps):
+        runner.step([StepEntry(r, [feeds[args.warmup + s][j]], [0]) for j, r in enumerate(ids)])
+    stop.record()
+    torch.cuda.synchronize()
+    decode_ms = start.elapsed_time(stop) / args.steps
+    launches = (ops.launch_count() - launches0) // args.steps
+    nbytes = runner.weight_bytes_per_step() + batch * (ctx_tokens + args.warmup + args.steps / 2) * runner.kv_bytes_per_token()
+    # what a design with routed experts and recurrent state reads besides: the experts a batch touches beyond one
+    # token's (at most all of them), and every request's state, read and written
+    for block in runner.model.blocks:
+        ffn = getattr(block, "feed_forward", None)
+        if hasattr(ffn, "experts"):
+            per_expert = (ffn.gate_up[0].numel() + ffn.down[0].numel()) * ffn.down.element_size()
+            nbytes += (min(ffn.experts, batch * ffn.top) - ffn.top) * per_expert
+    for entry, state in zip(runner.model.order, runner.store.state):
+        nbytes += 2 * batch * sum(t[0].numel() * t.element_size() for t in state.values())
+    out = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(T * 1000.0 / prefill_ms, 1),
+           "decode_ms": round(decode_ms, 4), "decode_tok_s": round(batch * 1000.0 / decode_ms, 1),
+           "decode_launches": int(launches), "decode_bytes_mb": round(nbytes / 1e6, 1),
+           "decode_hbm_frac": round(nbytes / (decode_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
+    runner.check()
+    del runner
+    torch.cuda.empty_cache()
+    return out
+
+
+
 def run_compare(args) -> int:
     import numpy as np
     import torch
@@ -394,55 +469,7 @@ def run_compare(args) -> int:
                     "mask_chunk": args.mask_chunk, "streams": args.streams, "share_kv": bool(args.share_kv), "sizes": {}}
 
     def measure(config: dict) -> dict:
-        folder = tempfile.mkdtemp(prefix="bench_compare_")
-        with open(os.path.join(folder, "config.json"), "w") as f:
-            json.dump(config, f)
-        pages = (batch * (ctx_tokens + args.steps + args.warmup + 16) + 2 * T) // page + 64
-        runner = ModelRunner(folder, dtype="bfloat16", page_size=page, num_pages=pages, max_num_seqs=max(batch, 4),
-                             max_model_len=8192, load_format="random", use_cuda_graphs=not args.no_graphs)
-        vocab = runner.config.vocab_size
-        # prefill: one prompt of T tokens in one step, as the captured graph a running engine replays; median of five
-        times = []
-        for w in range(getattr(runner, "mixed_graph_after", 0) + 2 + 5):
-            toks = rng.integers(0, vocab, T).tolist()
-            torch.cuda.synchronize()
-            time.sleep(0.2)  # a step by itself, as the burst peak it is compared with
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            runner.step([StepEntry(f"p{w}", toks, [T - 1])])
-            stop.record()
-            torch.cuda.synchronize()
-            runner.release(f"p{w}")
-            times.append(start.elapsed_time(stop))
-        prefill_ms = sorted(times[-5:])[2]
-        print(f"[bench]   prefill {prefill_ms:.3f} ms", file=sys.stderr, flush=True)
-        # decode: `batch` requests behind `ctx_tokens` cached tokens each
-        ids = [f"d{i}" for i in range(batch)]
-        per_step = max(1, 4096 // ctx_tokens)
-        for i in range(0, batch, per_step):
-            runner.step([StepEntry(r, rng.integers(0, vocab, ctx_tokens).tolist(), []) for r in ids[i:i + per_step]])
-        feeds = rng.integers(0, vocab, (args.steps + args.warmup, batch)).tolist()
-        for w in range(args.warmup):
-            runner.step([StepEntry(r, [feeds[w][j]], [0]) for j, r in enumerate(ids)])
-        torch.cuda.synchronize()
-        launches0 = ops.launch_count()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for s in range(args.steps):
-            runner.step([StepEntry(r, [feeds[args.warmup + s][j]], [0]) for j, r in enumerate(ids)])
-        stop.record()
-        torch.cuda.synchronize()
-        decode_ms = start.elapsed_time(stop) / args.steps
-        launches = (ops.launch_count() - launches0) // args.steps
-        nbytes = runner.weight_bytes_per_step() + batch * (ctx_tokens + args.warmup + args.steps / 2) * runner.kv_bytes_per_token()
-        out = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(T * 1000.0 / prefill_ms, 1),
-               "decode_ms": round(decode_ms, 4), "decode_tok_s": round(batch * 1000.0 / decode_ms, 1),
-               "decode_launches": int(launches), "decode_bytes_mb": round(nbytes / 1e6, 1),
-               "decode_hbm_frac": round(nbytes / (decode_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
-        runner.check()
-        del runner
-        torch.cuda.empty_cache()
-        return out
+        return measure_model(config, args, pk, rng)
 
     for name in (args.sizes.split(",") if args.sizes else COMPARE_SIZES):
         qwen, fokedra = compare_configs(COMPARE_SIZES[name], args.mask_chunk, args.streams, args.share_kv)
@@ -577,6 +604,213 @@ def run_compare(args) -> int:
     return 0
 
 
+def sarudra_config(z: dict, window: int) -> dict:
+    """config.json of a Sarudra decoder at the layer sizes ``z``: state-space layers and windowed attention layers in
+    turn; every feed-forward routed, two of eight experts of a quarter of the dense size beside a shared expert of
+    half of it, so that a token's feed-forward does the dense layer's work."""
+    heads = 2 * z["width"] // 64  # the state-space layers' inner width is twice the model's
+    groups = 8 if heads % 8 == 0 else 4
+    layers = []
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            kind, mixer = "mamba2", dict(heads=heads, vdim=64, state=128, groups=groups, conv=4, norm_groups=groups)
+        else:
+            kind, mixer = "attention", dict(dim=z["dim"], vdim=z["dim"], heads=z["heads"], kv_heads=z["kv_heads"],
+                                            scale=z["dim"] ** -0.5, softcap=50.0, mask=dict(size=window),
+                                            rot=dict(base=1000000.0, dims=z["dim"]))
+        mlp = dict(kind="moe", expert=dict(ff=z["ff"] // 4), router=dict(experts=8, top=2), shared=dict(ff=z["ff"] // 2))
+        layers.append(dict(type=kind, mixer=mixer, mlp=mlp))
+    return dict(architecture="Sarudra", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6, groups=4),
+                embedding=dict(scale=1.0), logit_softcap=30.0, layers=layers, max_position_embeddings=8192)
+
+
+def run_compare_sarudra(args) -> int:
+    """The Sarudra decoder beside the Qwen2.5 decoder at equal layer sizes (whole steps), then every kernel the design
+    adds, alone at the 7B layer sizes, beside its nearest relative of the Qwen2.5 path."""
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import ops
+    from slipstream_b200.engine.context import query_tiles_longest_first_host
+
+    pk, pk_kind = peaks()
+    rng = np.random.default_rng(0)
+    dev = torch.device("cuda:0")
+    batch, ctx_tokens, T, page = args.batch, args.prompt_len, args.chunk, 16
+    result: dict = {"compare": "sarudra", "peaks": pk_kind, "batch": batch, "context": ctx_tokens, "prefill_tokens": T,
+                    "window": args.window, "sizes": {}}
+    for name in (args.sizes.split(",") if args.sizes else COMPARE_SIZES):
+        qwen, _ = compare_configs(COMPARE_SIZES[name], 8192, 1, False)
+        result["sizes"][name] = {}
+        for which, config in (("qwen2", qwen), ("sarudra", sarudra_config(COMPARE_SIZES[name], args.window))):
+            if which == "qwen2" and args.skip_qwen2:
+                continue
+            print(f"[bench] {name} {which} ...", file=sys.stderr, flush=True)
+            result["sizes"][name][which] = measure_model(config, args, pk, rng)
+            print(f"[bench] {name} {which}: {result['sizes'][name][which]}", file=sys.stderr, flush=True)
+
+    print("[bench] single kernels ...", file=sys.stderr, flush=True)
+    z = COMPARE_SIZES["7b"]
+    h, n_q, n_kv, d, inter = z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"]
+    m = sarudra_config(z, args.window)["layers"][0]["mixer"]
+    s_heads, s_p, s_n, s_g, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+    inner, chans = s_heads * s_p, s_heads * s_p + 2 * s_g * s_n
+    experts, top, e_ff = 8, 2, inter // 4
+    gen = torch.Generator(device=dev).manual_seed(1)
+    COPIES = 6  # operands of each timed launch rotate through this many copies
+
+    def rand(*shape, dtype=torch.bfloat16, std=0.5):
+        return (torch.randn(*shape, generator=gen, device=dev) * std).to(dtype)
+
+    def sweep(run, copies=COPIES) -> float:
+        for i in range(copies):
+            run(i)
+        times = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(copies):
+                run(i)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / copies)
+        return sorted(times)[2]
+
+    kernels: dict = {}
+
+    def hbm(name: str, us: float, nbytes: float) -> None:
+        gbs = nbytes / (us * 1e-6) / 1e9
+        kernels[name] = {"us": round(us, 2), "gbs": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 3)}
+
+    def tensor(name: str, us: float, flops: float, peak_key: str = "bf16_tflops") -> None:
+        tf = flops / (us * 1e-6) / 1e12
+        kernels[name] = {"us": round(us, 2), "tflops": round(tf, 1), "bf16_frac": round(tf / pk[peak_key], 3)}
+
+    def step(q_lens, seq_lens):
+        starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+        as_dev = lambda v: torch.tensor(np.asarray(v), dtype=torch.int32, device=dev)  # noqa: E731
+        return types.SimpleNamespace(q_start=as_dev(starts), seq_lens=as_dev(seq_lens), state_slots=as_dev(np.arange(len(q_lens))),
+                                     num_requests=len(q_lens), is_decode_only=all(n == 1 for n in q_lens))
+
+    w_norm = rand(h, dtype=torch.float32)
+    w_norm_bf = w_norm.bfloat16()
+    for tokens, tag, ctx in ((T, "prefill", step([T], [T])), (batch, "decode", step([1] * batch, [ctx_tokens] * batch))):
+        res = [rand(tokens, h, dtype=torch.float32) for _ in range(COPIES)]
+        ys = [rand(tokens, h) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.add_rmsnorm(res[i], ys[i], w_norm_bf, 1e-6, torch.bfloat16))
+        hbm(f"{tag}_add_rmsnorm (qwen2)", us, tokens * h * (4 + 4 + 2 + 2))
+        us = sweep(lambda i: ops.group_norm(ys[i], w_norm, 4, 1e-6, torch.bfloat16, residual=res[i]))
+        hbm(f"{tag}_group_norm_add", us, tokens * h * (4 + 4 + 2 + 2))
+        # the sum over the chosen experts and the shared expert inside the same kernel
+        terms = [rand(tokens, top, h, dtype=torch.float32) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.group_norm(terms[i], w_norm, 4, 1e-6, torch.bfloat16, residual=res[i], terms=top, extra=ys[i]))
+        hbm(f"{tag}_group_norm_add of expert sum", us, tokens * h * (4 * top + 2 + 4 + 4 + 2))
+        del terms
+        width = (n_q + 2 * n_kv) * d
+        rows = [rand(tokens, width) for _ in range(COPIES)]
+        kvs = [torch.zeros((tokens + page - 1) // page + 1, 2, n_kv, page, d, dtype=torch.bfloat16, device=dev) for _ in range(COPIES)]
+        positions = torch.arange(tokens, dtype=torch.int32, device=dev)
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        qw = rand(d, dtype=torch.float32)
+        moved = tokens * d * 2.0 * (2 * n_q + 4 * n_kv)
+        us = sweep(lambda i: ops.rope_and_cache(rows[i], positions, positions, inv_freq, kvs[i], n_q, n_kv, d, d))
+        hbm(f"{tag}_rope_and_cache (qwen2)", us, moved)
+        us = sweep(lambda i: ops.norm_rope_cache(rows[i], positions, positions, kvs[i], n_q, n_kv, d, inv_freq=inv_freq, rotary_dim=d,
+                                                 value_inv_freq=inv_freq, value_rotary_dim=d, q_weight=qw, k_weight=qw, norm_dim=d, eps=1e-6))
+        hbm(f"{tag}_norm_rope_cache (q/k norm, rotated values)", us, moved)
+        outs = [rand(tokens, n_q * d) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.turn_heads(outs[i], positions, inv_freq, n_q, d, d))
+        hbm(f"{tag}_turn_heads", us, tokens * n_q * d * 4.0)
+        del rows, kvs, outs
+        # state-space mixer
+        proj_w = 2 * inner + 2 * s_g * s_n + s_heads
+        projs = [rand(tokens, proj_w) for _ in range(COPIES)]
+        w_taps, b_taps = rand(chans, taps, dtype=torch.float32), rand(chans, dtype=torch.float32)
+        conv_state = torch.zeros(ctx.num_requests, taps - 1, chans, device=dev)
+        us = sweep(lambda i: ops.conv_silu(projs[i], inner, chans, w_taps, b_taps, conv_state, ctx))
+        hbm(f"{tag}_conv_silu", us, tokens * chans * 4.0 + ctx.num_requests * (taps - 1) * chans * 8.0)
+        xbcs = [rand(tokens, chans) for _ in range(COPIES)]
+        dt_bias, a_log, d_skip = (rand(s_heads, dtype=torch.float32) for _ in range(3))
+        states = [torch.zeros(ctx.num_requests, s_heads, s_p, s_n, device=dev) for _ in range(COPIES)]
+        us = sweep(lambda i: ops.ssm_scan(xbcs[i], projs[i][:, inner + chans:], dt_bias, a_log, d_skip, states[i], ctx, s_heads, s_g, s_p, s_n))
+        state_bytes = ctx.num_requests * s_heads * s_p * s_n * 8.0
+        hbm(f"{tag}_ssm_scan", us, state_bytes + tokens * (chans * 2.0 + inner * 4.0))
+        kernels[f"{tag}_ssm_scan"]["fp32_tflops"] = round(6.0 * tokens * s_heads * s_p * s_n / us / 1e6, 2)
+        ysc = [rand(tokens, inner, dtype=torch.float32) for _ in range(COPIES)]
+        w_in = rand(inner, dtype=torch.float32)
+        us = sweep(lambda i: ops.group_norm(ysc[i], w_in, s_g, 1e-6, torch.bfloat16, gate=projs[i][:, :inner]))
+        hbm(f"{tag}_gated_group_norm", us, tokens * inner * 8.0)
+        del projs, xbcs, states, ysc
+        # routed experts: router, plan + gather + both grouped products; beside the dense gate/up + down of equal work
+        xs = [rand(tokens, h) for _ in range(COPIES)]
+        w_router = rand(experts, h, std=0.05)
+        us = sweep(lambda i: ops.router(xs[i], w_router, top))
+        kernels[f"{tag}_router"] = {"us": round(us, 2)}
+        ids, scores = ops.router(xs[0], w_router, top)
+        gate_up = [rand(experts, 2 * e_ff, h, std=0.02) for _ in range(2)]
+        down = [rand(experts, h, e_ff, std=0.02) for _ in range(2)]
+        before = ops.launch_count()
+        us = sweep(lambda i: ops.moe_experts(xs[i], ids, scores, gate_up[i % 2], down[i % 2]), copies=4)
+        touched = len(set(ids.flatten().tolist()))
+        if tag == "prefill":
+            tensor("prefill_routed_experts (plan, gather, up, down)", us, 6.0 * tokens * top * h * e_ff)
+        else:
+            hbm("decode_routed_experts (plan, gather, up, down)", us, touched * 3.0 * h * e_ff * 2)
+            kernels["decode_routed_experts (plan, gather, up, down)"]["experts_touched"] = touched
+        w_gu, w_d = [rand(2 * top * e_ff, h, std=0.02) for _ in range(2)], [rand(h, top * e_ff, std=0.02) for _ in range(2)]
+        us = sweep(lambda i: ops.linear(ops.gate_up_swiglu(xs[i], w_gu[i % 2], None, 64), w_d[i % 2]), copies=4)
+        if tag == "prefill":
+            tensor("prefill_dense gate/up + down of equal work (qwen2)", us, 6.0 * tokens * top * h * e_ff)
+        else:
+            hbm("decode_dense gate/up + down of equal work (qwen2)", us, 3.0 * h * top * e_ff * 2)
+        del gate_up, down, w_gu, w_d, xs
+
+    # attention: a window as long as the context, so that both designs do the same work
+    def tables(n_req: int, tokens: int) -> torch.Tensor:
+        per = (tokens + page - 1) // page
+        return torch.arange(n_req * per, dtype=torch.int32, device=dev).view(n_req, per)
+
+    kv_pages = [rand(batch * ((max(ctx_tokens, T) + page - 1) // page) + 1, 2, n_kv, page, d) for _ in range(COPIES)]
+    width = (n_q + 2 * n_kv) * d
+    qkv = rand(batch, width)
+    att = torch.empty(batch, n_q * d, dtype=torch.bfloat16, device=dev)
+    table = tables(batch, ctx_tokens)
+    q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+    lens = torch.full((batch,), ctx_tokens, dtype=torch.int32, device=dev)
+    slices = ops.decode_slices(batch, n_kv, n_q // n_kv, ctx_tokens, False, ops.sm_count(dev))
+    nbytes = batch * ctx_tokens * 2.0 * n_kv * d * 2 + 2.0 * batch * n_q * d * 2
+    stages = ops.functions.DECODE_RING_STAGES
+    us = sweep(lambda i: ops.paged_attention_decode(qkv, qkv.shape[1], att, kv_pages[i], table, q_start, lens, batch, n_q,
+                                                    n_kv, d, d ** -0.5, 0, slices, stages=stages))
+    hbm("decode_attention (qwen2: rotation outside here)", us, nbytes)
+    us = sweep(lambda i: ops.paged_attention_decode(qkv, qkv.shape[1], att, kv_pages[i], table, q_start, lens, batch, n_q,
+                                                    n_kv, d, d ** -0.5, ctx_tokens, slices, stages=stages, softcap=50.0))
+    hbm("decode_attention window + soft cap", us, nbytes)
+    qkv_p = rand(T, width)
+    att_p = torch.empty(T, n_q * d, dtype=torch.bfloat16, device=dev)
+    table_p, q_start_p = tables(1, T), torch.tensor([0, T], dtype=torch.int32, device=dev)
+    lens_p = torch.tensor([T], dtype=torch.int32, device=dev)
+    req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_longest_first_host(
+        np.asarray([T], dtype=np.int32), np.asarray([T], dtype=np.int32), 128 // (n_q // n_kv)))
+    flops = 4.0 * n_q * d * (T * (T + 1) // 2)
+    us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req, tok0,
+                                                             q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1))
+    tensor("prefill_attention tcgen05 (qwen2)", us, flops)
+    us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req, tok0,
+                                                             q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1, window=T, softcap=50.0))
+    tensor("prefill_attention tcgen05 window + soft cap", us, flops)
+    half = T // 4
+    flops_w = 4.0 * n_q * d * sum(min(t + 1, half) for t in range(T))
+    us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv_pages[i], table_p, req, tok0,
+                                                             q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1, window=half, softcap=50.0))
+    tensor(f"prefill_attention tcgen05 window of {half} + soft cap", us, flops_w)
+    ops.check_errors(dev)
+    result["kernels_7b"] = kernels
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -595,7 +829,8 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="run another measured workload end to end through the scheduler instead")
-    ap.add_argument("--compare", choices=["fokedra"], default=None,
+    ap.add_argument("--window", type=int, default=4096, help="--compare sarudra: positions of the sliding window")
+    ap.add_argument("--compare", choices=["fokedra", "sarudra"], default=None,
                     help="time another decoder design beside the Qwen2.5 decoder at equal layer sizes instead")
     ap.add_argument("--sizes", default="", help="--compare: which of 0.5b,7b,14b (default: all)")
     ap.add_argument("--mask-chunk", type=int, default=8192, help="--compare: positions per attention chunk")
@@ -615,7 +850,7 @@ def main() -> int:
         if args.steps == 256:
             args.steps = 64
         args.warmup = max(args.warmup, 3)
-        return run_compare(args)
+        return run_compare_sarudra(args) if args.compare == "sarudra" else run_compare(args)
     if args.workload:
         return run_workload(args.workload, args)
     if args.only in ("gemm", "attention"):

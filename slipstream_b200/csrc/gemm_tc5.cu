@@ -610,6 +610,15 @@ struct ManyArgs {
     int in_tiles;
     float in_eps;
     float act_alpha, act_limit, act_shift;  // as in GemmArgs
+    // Grouped form (grp_expert given): the rows of A are sorted by expert, B stacks the experts' weights (grp_b_rows
+    // rows each, N of them real), and a row tile is an entry of three lists of grp_tiles entries: the expert (-1: the
+    // entry holds nothing), the first row and the number of rows (at most 256; the rows behind them in the tile belong
+    // to the next expert and are computed but not stored).  C is in sorted order too.
+    const int32_t* grp_expert;
+    const int32_t* grp_row0;
+    const int32_t* grp_rows;
+    int grp_tiles;
+    int64_t grp_b_rows;
 };
 
 __device__ __forceinline__ float bias_many(const ManyArgs& g, int f) {
@@ -659,7 +668,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int rank = (int)cluster_rank();  // 0: the leader
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int bn = g.tile_cols;  // the tile's width: a multiple of 16 up to 256, chosen by the host so that the tiles fill the pairs
-    const int n_m = (g.M + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (g.N + bn - 1) / bn, n_tiles = n_m * n_n;
+    const int n_m = g.grp_expert ? g.grp_tiles : (g.M + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (g.N + bn - 1) / bn, n_tiles = n_m * n_n;
     const int k_iters = (g.K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -685,7 +694,13 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int it = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs) {
-            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * bn + rank * (bn / 2);
+            int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * bn + rank * (bn / 2);
+            if (g.grp_expert) {
+                const int e = g.grp_expert[t % n_m];
+                if (e < 0) continue;  // every role passes over the same entries
+                m0 = g.grp_row0[t % n_m] + rank * TC_BM;
+                n0 += (int)(e * g.grp_b_rows);
+            }
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, gave_up)) { ok = false; break; }
@@ -701,6 +716,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int it = 0, j = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
+            if (g.grp_expert && g.grp_expert[t % n_m] < 0) { --j; continue; }  // j counts the tiles that are computed
             const int buf = j & 1;
             if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -727,8 +743,14 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int j = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
+            if (g.grp_expert && g.grp_expert[t % n_m] < 0) { --j; continue; }
             const int buf = j & 1;
-            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * bn;
+            const int n0 = (t / n_m) * bn;
+            int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, m_end = g.M;
+            if (g.grp_expert) {
+                m0 = g.grp_row0[t % n_m] + rank * TC_BM;
+                m_end = g.grp_row0[t % n_m] + g.grp_rows[t % n_m];
+            }
             const int m = m0 + quarter * 32 + lane;
             // while the tile's products run: the scale of this thread's row (the norm in front), or the first
             // chunks of the stream that the row is added to
@@ -820,7 +842,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 for (int c = 0; c < bn; c += 16) {
                     uint32_t r[16];
                     tmem_ld16(acc + c, r);
-                    if (m >= g.M || n0 + c >= g.N) continue;
+                    if (m >= m_end || n0 + c >= g.N) continue;
                     if constexpr (ENDS == 2) {
 #pragma unroll
                         for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * rstd);
@@ -858,7 +880,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     tmem_ld16(acc + gc, gr);
                     tmem_ld16(acc + gc + 64, ur);
                     const int f0 = (n0 / 2) + c;
-                    if (m >= g.M || n0 + gc + 64 >= g.N) continue;
+                    if (m >= m_end || n0 + gc + 64 >= g.N) continue;
                     uint32_t packed[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
@@ -1176,6 +1198,7 @@ static int gemm_tc5_many(const void* A, const void* B, const void* bias, int bia
     g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
     g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
     g.act_alpha = ends.act_alpha; g.act_limit = ends.act_limit; g.act_shift = ends.act_shift;
+    g.grp_expert = g.grp_row0 = g.grp_rows = nullptr; g.grp_tiles = 0; g.grp_b_rows = 0;
     const int tiles2 = n_m * ((N + bn - 1) / bn);
     const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
     if (ends.residual) return launch_pair<1>(ma, mb, g, pairs, stream);
@@ -1187,6 +1210,38 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
                                 int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
                                 int* err, cudaStream_t stream) {
     return gemm_tc5_many(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, out_f32, swiglu, tile_cols, NormEnds(), err, stream);
+}
+
+// The grouped form of the two-SM kernel, for routed experts.  A [total_rows, K]: the activations sorted by expert;
+// B [experts * b_rows, K]: the experts' weights stacked; C [total_rows, N (N / 2 with swiglu)] in sorted order,
+// bfloat16.  The three lists (n_tiles entries, written on the device by the plan of the step) name each row tile's
+// expert, first row and number of rows.  swiglu: an expert's rows alternate 64 gate and 64 up features.
+extern "C" int ss_gemm_tc5_grouped(const void* A, const void* B, void* C, int total_rows, int N, int K, int experts,
+                                   int64_t b_rows, int64_t ldc, int swiglu, const int32_t* tile_expert,
+                                   const int32_t* tile_row0, const int32_t* tile_rows, int n_tiles, int* err,
+                                   cudaStream_t stream) {
+    if (total_rows <= 0 || N <= 0 || n_tiles <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ldc % 8 != 0 || N % 16 != 0) return -2003;
+    if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -2004;
+    if (swiglu && N % 128 != 0) return -2007;
+    if (!tile_expert || !tile_row0 || !tile_rows || b_rows < N) return -2010;
+    const int bn = MT_BN;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, total_rows, K, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, (int64_t)experts * b_rows, K, K, bn / 2);
+    if (rc) return rc;
+    ManyArgs g;
+    g.C = C; g.bias = nullptr; g.err = err; g.M = total_rows; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = 0;
+    g.bias_f32 = 0; g.swiglu = swiglu; g.tile_cols = bn;
+    g.residual = nullptr; g.tile_squares = nullptr; g.scaled = nullptr; g.norm_weight = nullptr; g.norm_w_f32 = 0;
+    g.in_squares = nullptr; g.in_tiles = 0; g.in_eps = 0.f;
+    g.act_alpha = 1.f; g.act_limit = 0.f; g.act_shift = 0.f;
+    g.grp_expert = tile_expert; g.grp_row0 = tile_row0; g.grp_rows = tile_rows; g.grp_tiles = n_tiles; g.grp_b_rows = b_rows;
+    const int n_sms = ss_sm_count();
+    const int max_pairs = n_sms / 2 > 0 ? n_sms / 2 : 1;
+    const int tiles2 = n_tiles * ((N + bn - 1) / bn);
+    return launch_pair<0>(ma, mb, g, tiles2 < max_pairs ? tiles2 : max_pairs, stream);
 }
 
 // The same product with the fused gated unit of other constants than SwiGLU's.

@@ -29,13 +29,21 @@ __device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-
 // the row in `groups` equal consecutive parts; y_i = x_i / sqrt(mean(part^2) + eps) * weight[i]
 // residual given: residual[row][i] += y_i and out (if given) = residual; else out = y.
 // rows given: source row of output row m is rows[m].
+// term_rows given: term k of row r is row term_rows[r * terms + k] of `in` ([.][hidden]) instead.
 // A block per output row; a group is summed by GW warps in a fixed order that depends on the sizes only.
+template <typename TI>
+__device__ __forceinline__ float term_at(const TI* __restrict__ in, const TI* __restrict__ src,
+                                         const int32_t* __restrict__ term_rows, int64_t row, int terms, int hidden, int k, int i) {
+    if (term_rows) return to_float(in[(int64_t)term_rows[row * terms + k] * hidden + i]);
+    return to_float(src[(int64_t)k * hidden + i]);
+}
+
 template <typename TI, typename TG, typename TO>
 __global__ void __launch_bounds__(256)
 group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const TO* __restrict__ extra,
                   const TG* __restrict__ gate, int64_t gate_stride, const float* __restrict__ weight,
                   float* __restrict__ residual, TO* __restrict__ out, const int32_t* __restrict__ rows, int hidden,
-                  int groups, float eps) {
+                  int groups, float eps, const int32_t* __restrict__ term_rows) {
     pdl_wait();
     __shared__ float part[8];
     const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -51,8 +59,8 @@ group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const
         if (on) {
             for (int j = wi * 32 + lane; j < gs; j += gw * 32) {
                 const int i = g * gs + j;
-                float x = to_float(src[i]);
-                for (int k = 1; k < terms; ++k) x += to_float(src[(int64_t)k * hidden + i]);
+                float x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
+                for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
                 if (extra) x += to_float(extra[row * hidden + i]);
                 if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
                 ss = fmaf(x, x, ss);
@@ -68,8 +76,8 @@ group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const
             const float rstd = 1.0f / sqrtf(total / (float)gs + eps);
             for (int j = wi * 32 + lane; j < gs; j += gw * 32) {
                 const int i = g * gs + j;
-                float x = to_float(src[i]);
-                for (int k = 1; k < terms; ++k) x += to_float(src[(int64_t)k * hidden + i]);
+                float x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
+                for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
                 if (extra) x += to_float(extra[row * hidden + i]);
                 if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
                 float y = x * rstd * weight[i];
@@ -86,12 +94,13 @@ group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const
 // in_type: 0 the compute type, 1 float32.  dtype: the compute type (of out, extra and gate).
 extern "C" int ss_group_norm(const void* in, int in_f32, int64_t in_stride, int terms, const void* extra, const void* gate,
                              int64_t gate_stride, const float* weight, float* residual, void* out, const int32_t* rows,
-                             int n_out, int hidden, int groups, float eps, int dtype, cudaStream_t stream) {
+                             int n_out, int hidden, int groups, float eps, int dtype, cudaStream_t stream,
+                             const int32_t* term_rows) {
     if (n_out <= 0) return 0;
     if (groups < 1 || hidden % groups || terms < 1) return (int)cudaErrorInvalidValue;
 #define GN_GO(TI, T)                                                                                                  \
     ss_launch(group_norm_kernel<TI, T, T>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms,        \
-              (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps)
+              (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows)
     if (dtype == SS_F32) GN_GO(float, float);
     else if (in_f32) GN_GO(float, bf16);
     else GN_GO(bf16, bf16);
@@ -408,7 +417,7 @@ extern "C" int ss_router(const void* x, const void* w_router, int32_t* ids, floa
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ perm, int32_t* __restrict__ tile_expert,
                 int32_t* __restrict__ tile_row0, int32_t* __restrict__ tile_rows, int A, int experts, int tile,
-                int max_tiles) {
+                int max_tiles, int32_t* __restrict__ place) {
     pdl_wait();
     __shared__ int count[ROUTER_MAX_EXPERTS], start[ROUTER_MAX_EXPERTS], first_tile[ROUTER_MAX_EXPERTS + 1];
     const int tid = threadIdx.x;
@@ -445,17 +454,19 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ perm, int
     __syncthreads();
     for (int a = tid; a < A; a += blockDim.x) {
         const int e = ids[a];
-        perm[start[e] + atomicAdd(&count[e], 1)] = a;
+        const int at = start[e] + atomicAdd(&count[e], 1);
+        perm[at] = a;
+        if (place) place[a] = at;  // the inverse: where assignment a stands in sorted order
     }
 }
 
 extern "C" int ss_moe_plan(const int32_t* ids, int32_t* perm, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows,
-                           int A, int experts, int tile, int max_tiles, cudaStream_t stream) {
+                           int A, int experts, int tile, int max_tiles, int32_t* place, cudaStream_t stream) {
     if (A <= 0) return 0;
     if (experts < 1 || experts > ROUTER_MAX_EXPERTS || tile < 1 || max_tiles < (A + tile - 1) / tile + experts)
         return (int)cudaErrorInvalidValue;
     ss_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, perm, tile_expert, tile_row0, tile_rows, A, experts, tile,
-              max_tiles);
+              max_tiles, place);
     return SS_LAUNCH_CHECK();
 }
 
@@ -474,7 +485,7 @@ __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, const T* __restrict__ W,
                 const int32_t* __restrict__ perm, const int32_t* __restrict__ tile_expert,
                 const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_rows, T* __restrict__ hidden,
-                float* __restrict__ y, int top, int K, int n_out) {
+                float* __restrict__ y, int top, int K, int n_out, int run) {
     pdl_wait();
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
@@ -512,8 +523,10 @@ moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, cons
             }
             As[lk + q][lr] = a;
             const int wn = n0 + lr;
-            Ws[0][lk + q][lr] = (wn < n_out && k < K) ? to_float(We[(int64_t)wn * K + k]) : 0.f;
-            if (UP) Ws[1][lk + q][lr] = (wn < n_out && k < K) ? to_float(We[(int64_t)(n_out + wn) * K + k]) : 0.f;
+            // UP: gate and up rows alternate in runs of `run` (run = n_out: all gate rows, then all up rows)
+            const int64_t wrow = UP ? (int64_t)(wn / run) * 2 * run + wn % run : wn;
+            Ws[0][lk + q][lr] = (wn < n_out && k < K) ? to_float(We[wrow * K + k]) : 0.f;
+            if (UP) Ws[1][lk + q][lr] = (wn < n_out && k < K) ? to_float(We[(wrow + run) * K + k]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -549,12 +562,13 @@ moe_gemm_kernel(const T* __restrict__ x, const float* __restrict__ weights, cons
 
 extern "C" int ss_moe_gemm(const void* x, const float* weights, const void* W, const int32_t* perm,
                            const int32_t* tile_expert, const int32_t* tile_row0, const int32_t* tile_rows, void* hidden,
-                           float* y, int top, int K, int n_out, int max_tiles, int up, int dtype, cudaStream_t stream) {
+                           float* y, int top, int K, int n_out, int max_tiles, int up, int dtype, int run, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
+    if (up && (run < 1 || n_out % run)) return (int)cudaErrorInvalidValue;
     const dim3 grid(max_tiles, (n_out + MG_N - 1) / MG_N);
 #define MG_GO(T, UP)                                                                                                    \
     ss_launch(moe_gemm_kernel<T, UP>, grid, dim3(256), 0, stream, (const T*)x, weights, (const T*)W, perm, tile_expert,       \
-              tile_row0, tile_rows, (T*)hidden, y, top, K, n_out)
+              tile_row0, tile_rows, (T*)hidden, y, top, K, n_out, run)
     if (dtype == SS_BF16) { if (up) MG_GO(bf16, true); else MG_GO(bf16, false); }
     else { if (up) MG_GO(float, true); else MG_GO(float, false); }
 #undef MG_GO
@@ -618,7 +632,7 @@ __global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, const int32_t* __restrict__ perm,
                     const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_row0,
                     const int32_t* __restrict__ tile_rows, bf16* __restrict__ hidden, float* __restrict__ y, int K,
-                    int n_out) {
+                    int n_out, int run) {
     constexpr int WARPS_N = 8 / WARPS_M, TM = BM / WARPS_M, TN = 64 / WARPS_N, MT = TM / 16, NT = TN / 8;
     constexpr int NB = UP ? 128 : 64, U = UP ? 2 : 1;
     static_assert(TM % 16 == 0 && TN % 16 == 0, "a warp's tile is whole m16 x n16 pieces");
@@ -645,7 +659,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, cons
             const int r = c >> 2, kc = (c & 3) * 8;
             const int n = n0 + (r & 63);
             const bool on = n < n_out && k0 + kc < K;
-            const int64_t wrow = (UP && r >= 64) ? n_out + n : n;  // gate rows, then the matching up rows
+            // UP: gate and up rows alternate in runs of `run`; rows 0..63 of the tile are gate rows, 64..127 the up rows
+            const int64_t wrow = UP ? (int64_t)(n / run) * 2 * run + n % run + (r >= 64 ? run : 0) : n;
             cp_async_16(bs + r * MM_STR + kc, We + (on ? wrow * K + k0 + kc : 0), on);
         }
     };
@@ -718,12 +733,12 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, cons
 template <int BM, int WARPS_M, bool UP>
 static int launch_moe_mma(const void* A, const void* W, const int32_t* perm, const int32_t* tile_expert,
                           const int32_t* tile_row0, const int32_t* tile_rows, void* hidden, float* y, int K, int n_out,
-                          int max_tiles, cudaStream_t stream) {
+                          int max_tiles, int run, cudaStream_t stream) {
     constexpr int smem = moe_mma_smem<BM, UP>();
     static SsPerDevice opted;
     if (int rc = ss_opt_in_smem(moe_gemm_mma_kernel<BM, WARPS_M, UP>, smem, opted)) return rc;
     ss_launch(moe_gemm_mma_kernel<BM, WARPS_M, UP>, dim3(max_tiles, (n_out + 63) / 64), dim3(256), smem, stream,
-              (const bf16*)A, (const bf16*)W, perm, tile_expert, tile_row0, tile_rows, (bf16*)hidden, y, K, n_out);
+              (const bf16*)A, (const bf16*)W, perm, tile_expert, tile_row0, tile_rows, (bf16*)hidden, y, K, n_out, run);
     return SS_LAUNCH_CHECK();
 }
 
@@ -731,15 +746,16 @@ static int launch_moe_mma(const void* A, const void* W, const int32_t* perm, con
 // hidden rows and the output one float32 row per assignment.
 extern "C" int ss_moe_gemm_mma(const void* A, const void* W, const int32_t* perm, const int32_t* tile_expert,
                                const int32_t* tile_row0, const int32_t* tile_rows, void* hidden, float* y, int K, int n_out,
-                               int max_tiles, int tile, int up, cudaStream_t stream) {
+                               int max_tiles, int tile, int up, int run, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
+    if (up && (run < 1 || n_out % run)) return (int)cudaErrorInvalidValue;
     if (K % 8 || n_out % 8 || (tile != 128 && tile != 32) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
         return (int)cudaErrorInvalidValue;
     if (tile == 128)
-        return up ? launch_moe_mma<128, 4, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream)
-                  : launch_moe_mma<128, 4, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream);
-    return up ? launch_moe_mma<32, 2, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream)
-              : launch_moe_mma<32, 2, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, stream);
+        return up ? launch_moe_mma<128, 4, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
+                  : launch_moe_mma<128, 4, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
+    return up ? launch_moe_mma<32, 2, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
+              : launch_moe_mma<32, 2, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
 }
 
 extern "C" int ss_moe_gather(const void* x, const float* weights, const int32_t* perm, void* sorted, int total, int top,
@@ -756,27 +772,29 @@ extern "C" int ss_moe_gather(const void* x, const float* weights, const int32_t*
 // choices, then the shared expert's.
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ shared, T* __restrict__ out,
-                                   int64_t n, int hidden, int top) {
+                                   int64_t n, int hidden, int top, const bf16* __restrict__ sorted,
+                                   const int32_t* __restrict__ place) {
     pdl_wait();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     const int64_t t = idx / hidden;
     const int i = (int)(idx - t * hidden);
     float v = 0.f;
-    for (int k = 0; k < top; ++k) v += y[(t * top + k) * hidden + i];
+    for (int k = 0; k < top; ++k)  // float32 rows in the order of the choices, or bfloat16 rows in sorted order
+        v += sorted ? to_float(sorted[(int64_t)place[t * top + k] * hidden + i]) : y[(t * top + k) * hidden + i];
     if (shared) v += to_float(shared[idx]);
     out[idx] = from_float<T>(v);
 }
 
 extern "C" int ss_moe_combine(const float* y, const void* shared, void* out, int n_tokens, int hidden, int top, int dtype,
-                              cudaStream_t stream) {
+                              const void* sorted, const int32_t* place, cudaStream_t stream) {
     const int64_t n = (int64_t)n_tokens * hidden;
     if (n <= 0) return 0;
     const dim3 grid((unsigned)((n + 255) / 256));
     if (dtype == SS_BF16)
-        ss_launch(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, y, (const bf16*)shared, (bf16*)out, n, hidden, top);
+        ss_launch(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, y, (const bf16*)shared, (bf16*)out, n, hidden, top, (const bf16*)sorted, place);
     else
-        ss_launch(moe_combine_kernel<float>, grid, dim3(256), 0, stream, y, (const float*)shared, (float*)out, n, hidden, top);
+        ss_launch(moe_combine_kernel<float>, grid, dim3(256), 0, stream, y, (const float*)shared, (float*)out, n, hidden, top, (const bf16*)nullptr, (const int32_t*)nullptr);
     return SS_LAUNCH_CHECK();
 }
 

@@ -60,20 +60,20 @@ _OPS_SIGNATURES = {
     "ss_glu_limited": [c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
     "ss_sigmoid_gate": [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p],
     "ss_group_norm": [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_int, c_int, c_int, c_float, c_int, c_void_p],
+                      c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ss_round_stream": [c_void_p, c_void_p, c_int64, c_void_p],
     "ss_conv_silu": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_ssm_scan": [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_router": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                    c_int, c_int, c_int, c_int, c_void_p],
+                    c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ss_moe_gemm_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_int, c_void_p],
+                        c_int, c_int, c_int, c_void_p],
     "ss_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "ss_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ss_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "ss_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_void_p,
                            c_void_p],
@@ -120,6 +120,8 @@ _GEMM_SIGNATURES = {
     "ss_gemm_tc5_scaled_glu": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                c_int64, c_int64, c_int64, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p,
                                c_void_p, c_void_p],
+    "ss_gemm_tc5_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p,
+                            c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                            c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -1377,12 +1379,14 @@ def gate_up_glu(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: tor
 
 def group_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype, *,
                residual: torch.Tensor | None = None, rows: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-               terms: int = 1, extra: torch.Tensor | None = None, want_out: bool = True) -> torch.Tensor | None:
+               terms: int = 1, extra: torch.Tensor | None = None, want_out: bool = True,
+               term_rows: torch.Tensor | None = None) -> torch.Tensor | None:
     """RMS norm in ``groups`` equal consecutive parts of the last axis, each part over its own root mean square
     (``v / sqrt(mean(v^2) + eps)``), times ``weight`` (float32 [hidden]); float32 arithmetic, one rounding.
 
     ``x`` [N, hidden] in ``out_dtype`` or float32.  ``terms`` > 1: ``x`` is [N, terms, hidden] (float32) and the
-    terms are summed first; ``extra`` [N, hidden] (``out_dtype``) is added to that sum.  ``gate`` (a view [N, hidden]
+    terms are summed first; ``extra`` [N, hidden] (``out_dtype``) is added to that sum.  ``term_rows`` (int32
+    [N * terms]): ``x`` is [any, hidden] and term k of row r is its row ``term_rows[r * terms + k]``.  ``gate`` (a view [N, hidden]
     with unit inner stride, ``out_dtype``): the input is multiplied by ``silu(gate)`` before the norm.
     ``residual`` (float32 [N, hidden]): the result is ADDED to it in place, and what is returned is the new
     residual rounded to ``out_dtype`` (nothing with ``want_out`` False).  ``rows`` (int32 [M]): only those rows
@@ -1391,11 +1395,15 @@ def group_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, o
     _need(weight, torch.float32, "norm weight")
     if x.dtype not in (out_dtype, torch.float32) or not x.is_cuda or not x.is_contiguous():
         raise KernelError("group_norm takes a contiguous CUDA tensor in the compute dtype or float32")
-    if terms > 1 and (x.dim() != 3 or x.shape[1] != terms or x.dtype != torch.float32):
+    if term_rows is not None:
+        _need(term_rows, torch.int32, "term_rows")
+        if x.dim() != 2 or term_rows.numel() % terms:
+            raise KernelError("with term_rows, x must be [rows, hidden] and term_rows hold N * terms entries")
+    elif terms > 1 and (x.dim() != 3 or x.shape[1] != terms or x.dtype != torch.float32):
         raise KernelError("with terms, x must be float32 [N, terms, hidden]")
     if x.shape[-1] != hidden or groups < 1 or hidden % groups:
         raise KernelError(f"group_norm: {hidden} features do not split into {groups} groups, or x is of another width")
-    n = x.shape[0]
+    n = x.shape[0] if term_rows is None else term_rows.numel() // terms
     n_out = n if rows is None else rows.numel()
     if rows is not None:
         _need(rows, torch.int32, "rows")
@@ -1415,7 +1423,8 @@ def group_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, o
     out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if want_out else None
     _check(ops_library().ss_group_norm(x.data_ptr(), int(x.dtype == torch.float32), terms * hidden, int(terms), _ptr(extra),
                                        _ptr(gate), gate_stride, weight.data_ptr(), _ptr(residual), _ptr(out), _ptr(rows),
-                                       n_out, hidden, int(groups), float(eps), _code(out_dtype), _stream()), "group_norm")
+                                       n_out, hidden, int(groups), float(eps), _code(out_dtype), _stream(), _ptr(term_rows)),
+           "group_norm")
     return out
 
 
@@ -1503,65 +1512,92 @@ def router(x: torch.Tensor, weight: torch.Tensor, top: int, renormalize: bool = 
 MOE_TILE = 64  # rows of one expert that a block of the grouped products takes
 
 
+GROUPED_TCGEN05_ROWS = 1024  # from this many (token, choice) pairs the experts' products run the two-SM tcgen05 kernel
+
+
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
-                ) -> torch.Tensor:
+                run: int | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
     """The chosen experts of every token: ``y[t, k] = W_down[e] (silu(W_gate[e] a) * (W_up[e] a))`` with
     ``e = ids[t, k]`` and ``a = scores[t, k] * x[t]`` (the score multiplies the expert's INPUT), rounded to the
-    compute dtype.  ``gate_up`` [experts, 2 ff, hidden] (gate rows, then up rows), ``down`` [experts, hidden, ff].
-    Returns float32 [N, top, hidden].  The same launches whatever the routing: the plan (assignments sorted by expert
-    and cut into tiles), the up product with the activation, the down product.  bfloat16 with sizes in steps of 8
-    runs the products on the tensor cores (tiles of 128 sorted rows when experts get many rows each, of 32 otherwise),
-    behind a gather of the scaled activations into sorted order; everything else runs them on CUDA cores."""
+    compute dtype.  ``gate_up`` [experts, 2 ff, hidden]: gate and up rows alternating in runs of ``run`` (default ff:
+    all gate rows, then all up rows); ``down`` [experts, hidden, ff].
+
+    Returns (terms, term_rows): either float32 [N, top, hidden] and None, or, from the tcgen05 path, bfloat16
+    [N * top, hidden] in sorted order with int32 [N * top] saying where pair (t, k) stands (`group_norm` and
+    `moe_combine` take both forms).  The same launches whatever the routing: the plan (pairs sorted by expert and cut
+    into tiles), a gather of the scaled activations into sorted order, the up product with the activation, the down
+    product.  bfloat16 with sizes in steps of 8 runs the products on the tensor cores: mma.sync tiles of 32 or 128
+    sorted rows, or, with runs of 64 and many pairs, the grouped form of the two-SM tcgen05 kernel over tiles of 256;
+    everything else runs them on CUDA cores."""
     n, hidden = x.shape
     experts, two_ff, _ = gate_up.shape
     ff, top = two_ff // 2, ids.shape[1]
+    run = ff if run is None else int(run)
     _need(x, None, "x")
     _need(gate_up, x.dtype, "gate_up")
     _need(down, x.dtype, "down")
     _need(ids, torch.int32, "ids")
     _need(scores, torch.float32, "scores")
-    if tuple(down.shape) != (experts, hidden, ff) or gate_up.shape[2] != hidden:
+    if tuple(down.shape) != (experts, hidden, ff) or gate_up.shape[2] != hidden or run < 1 or ff % run:
         raise KernelError("moe_experts: weights of the wrong shape")
     a = n * top
     tensor_cores = x.dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0
-    tile = MOE_TILE if not tensor_cores else (128 if a >= 96 * experts else 32)
+    tcgen05 = tensor_cores and run == 64 and hidden % 16 == 0 and a >= GROUPED_TCGEN05_ROWS
+    tile = MOE_TILE if not tensor_cores else (256 if tcgen05 else (128 if a >= 96 * experts else 32))
     max_tiles = (a + tile - 1) // tile + experts
-    plan = torch.empty(a + 3 * max_tiles, dtype=torch.int32, device=x.device)
-    perm, tile_expert = plan[:a], plan[a: a + max_tiles]
-    tile_row0, tile_rows = plan[a + max_tiles: a + 2 * max_tiles], plan[a + 2 * max_tiles:]
+    plan = torch.empty(2 * a + 3 * max_tiles, dtype=torch.int32, device=x.device)
+    perm, place, tile_expert = plan[:a], plan[a: 2 * a], plan[2 * a: 2 * a + max_tiles]
+    tile_row0, tile_rows = plan[2 * a + max_tiles: 2 * a + 2 * max_tiles], plan[2 * a + 2 * max_tiles:]
     lib = ops_library()
     _check(lib.ss_moe_plan(ids.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
-                           tile_rows.data_ptr(), a, experts, tile, max_tiles, _stream()), "moe_plan")
+                           tile_rows.data_ptr(), a, experts, tile, max_tiles, place.data_ptr(), _stream()), "moe_plan")
     hidden_act = torch.empty((a, ff), dtype=x.dtype, device=x.device)
-    y = torch.empty((n, top, hidden), dtype=torch.float32, device=x.device)
+    lists = (perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr())
     if tensor_cores:
-        lists = (perm.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr())
         gathered = torch.empty((a, hidden), dtype=x.dtype, device=x.device)
         _check(lib.ss_moe_gather(x.data_ptr(), scores.data_ptr(), perm.data_ptr(), gathered.data_ptr(), a, top, hidden,
                                  _stream()), "moe_gather")
+    if tcgen05:
+        err = error_word(x.device).data_ptr()
+        y_sorted = torch.empty((a, hidden), dtype=x.dtype, device=x.device)
+        _check(gemm_library().ss_gemm_tc5_grouped(gathered.data_ptr(), gate_up.data_ptr(), hidden_act.data_ptr(), a, two_ff,
+                                                  hidden, experts, two_ff, ff, 1, *lists[1:], max_tiles, err, _stream()),
+               "moe_up")
+        _check(gemm_library().ss_gemm_tc5_grouped(hidden_act.data_ptr(), down.data_ptr(), y_sorted.data_ptr(), a, hidden, ff,
+                                                  experts, hidden, hidden, 0, *lists[1:], max_tiles, err, _stream()),
+               "moe_down")
+        return y_sorted, place
+    y = torch.empty((n, top, hidden), dtype=torch.float32, device=x.device)
+    if tensor_cores:
         _check(lib.ss_moe_gemm_mma(gathered.data_ptr(), gate_up.data_ptr(), *lists, hidden_act.data_ptr(), None, hidden, ff,
-                                   max_tiles, tile, 1, _stream()), "moe_up")
+                                   max_tiles, tile, 1, run, _stream()), "moe_up")
         _check(lib.ss_moe_gemm_mma(hidden_act.data_ptr(), down.data_ptr(), *lists, None, y.data_ptr(), ff, hidden,
-                                   max_tiles, tile, 0, _stream()), "moe_down")
-        return y
-    _check(lib.ss_moe_gemm(x.data_ptr(), scores.data_ptr(), gate_up.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(),
-                           tile_row0.data_ptr(), tile_rows.data_ptr(), hidden_act.data_ptr(), None, top, hidden, ff,
-                           max_tiles, 1, _code(x.dtype), _stream()), "moe_up")
-    _check(lib.ss_moe_gemm(hidden_act.data_ptr(), None, down.data_ptr(), perm.data_ptr(), tile_expert.data_ptr(),
-                           tile_row0.data_ptr(), tile_rows.data_ptr(), None, y.data_ptr(), top, ff, hidden,
-                           max_tiles, 0, _code(x.dtype), _stream()), "moe_down")
-    return y
+                                   max_tiles, tile, 0, 0, _stream()), "moe_down")
+        return y, None
+    _check(lib.ss_moe_gemm(x.data_ptr(), scores.data_ptr(), gate_up.data_ptr(), *lists, hidden_act.data_ptr(), None, top,
+                           hidden, ff, max_tiles, 1, _code(x.dtype), run, _stream()), "moe_up")
+    _check(lib.ss_moe_gemm(hidden_act.data_ptr(), None, down.data_ptr(), *lists, None, y.data_ptr(), top, ff, hidden,
+                           max_tiles, 0, _code(x.dtype), 0, _stream()), "moe_down")
+    return y, None
 
 
-def moe_combine(y: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, shared: torch.Tensor | None, out_dtype: torch.dtype,
+                term_rows: torch.Tensor | None = None, top: int = 1) -> torch.Tensor:
     """``sum_k y[t, k] + shared[t]`` rounded to ``out_dtype``: the chosen experts' outputs in the order of the choices,
-    then the shared expert's."""
-    _need(y, torch.float32, "expert outputs")
-    n, top, hidden = y.shape
+    then the shared expert's.  ``y``: either form that `moe_experts` returns (with ``term_rows``: the sorted
+    bfloat16 rows, ``top`` choices a token)."""
+    if term_rows is None:
+        _need(y, torch.float32, "expert outputs")
+        n, top, hidden = y.shape
+    else:
+        _need(y, torch.bfloat16, "sorted expert outputs")
+        _need(term_rows, torch.int32, "term_rows")
+        n, hidden = term_rows.numel() // top, y.shape[1]
     if shared is not None:
         _need(shared, out_dtype, "shared expert output")
     out = torch.empty((n, hidden), dtype=out_dtype, device=y.device)
-    _check(ops_library().ss_moe_combine(y.data_ptr(), _ptr(shared), out.data_ptr(), n, hidden, top, _code(out_dtype),
+    _check(ops_library().ss_moe_combine(y.data_ptr() if term_rows is None else None, _ptr(shared), out.data_ptr(), n, hidden,
+                                        top, _code(out_dtype), _ptr(y) if term_rows is not None else None, _ptr(term_rows),
                                         _stream()), "moe_combine")
     return out
 

@@ -86,8 +86,8 @@ class BranchNormBlock(Block):
             else:
                 out = self.feed_forward.forward(x, ctx)
             if isinstance(out, dict):  # a feed-forward whose output is a sum it has not formed: the norm's kernel does
-                x = self.ffn_norm.add_branch(residual, out["terms"], terms=out["terms"].shape[1], extra=out.get("extra"),
-                                             want_out=hand_over)
+                x = self.ffn_norm.add_branch(residual, out["terms"], terms=out["count"], extra=out.get("extra"),
+                                             term_rows=out.get("term_rows"), want_out=hand_over)
             else:
                 x = self.ffn_norm.add_branch(residual, out, want_out=hand_over)
         return residual, None, (x if hand_over else None)

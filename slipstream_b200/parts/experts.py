@@ -57,8 +57,16 @@ class RoutedExperts(FeedForward):
         super().bind(weights, runtime)
         name = self.expert_names.format
         self.router_weight = weights[self.router_tensor]
-        self.gate_up = torch.stack([torch.cat([weights[name(e=e, role="gate")], weights[name(e=e, role="up")]], dim=0)
-                                    for e in range(self.experts)]).contiguous()
+        # gate and up rows alternate in runs of `run`, so that a tile of the stacked product holds 64 gate features and
+        # the 64 matching up features (the tcgen05 kernel's fused activation needs both in one block)
+        f = self.expert_size
+        self.run = 64 if f % 64 == 0 else f
+
+        def stacked(e: int) -> torch.Tensor:
+            g, u = weights[name(e=e, role="gate")], weights[name(e=e, role="up")]
+            return torch.stack([g.reshape(f // self.run, self.run, -1), u.reshape(f // self.run, self.run, -1)], dim=1).reshape(2 * f, -1)
+
+        self.gate_up = torch.stack([stacked(e) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([weights[name(e=e, role="down")] for e in range(self.experts)]).contiguous()
 
     def weight_bytes(self) -> int:
@@ -68,8 +76,8 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx, as_terms: bool = False):
         ids, scores = ops.router(x, self.router_weight, self.top, self.renormalize)
-        y = ops.moe_experts(x, ids, scores, self.gate_up, self.down)
+        y, term_rows = ops.moe_experts(x, ids, scores, self.gate_up, self.down, self.run)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         if as_terms:
-            return {"terms": y, "extra": shared}
-        return ops.moe_combine(y, shared, self.runtime.dtype)
+            return {"terms": y, "extra": shared, "term_rows": term_rows, "count": self.top}
+        return ops.moe_combine(y, shared, self.runtime.dtype, term_rows, self.top)

@@ -86,13 +86,14 @@ class GroupRMSNorm(Norm):
         return ops.group_norm(residual, self.weight, self.groups, self.eps, self.runtime.dtype, rows=rows)
 
     def add_branch(self, residual: torch.Tensor, y: torch.Tensor, *, gate: torch.Tensor | None = None, terms: int = 1,
-                   extra: torch.Tensor | None = None, want_out: bool = True) -> torch.Tensor | None:
+                   extra: torch.Tensor | None = None, term_rows: torch.Tensor | None = None,
+                   want_out: bool = True) -> torch.Tensor | None:
         """``residual += norm(y)`` in place; returns the new stream as a branch reads it (the stream itself in
         float32, its rounding in bfloat16; None with ``want_out`` False).  ``terms`` / ``extra``: ``y`` is a sum that
         has not been formed yet (`ops.group_norm`)."""
         fp32 = self.runtime.dtype == torch.float32
         out = ops.group_norm(y, self.weight, self.groups, self.eps, self.runtime.dtype, residual=residual, gate=gate,
-                             terms=terms, extra=extra, want_out=want_out and not fp32)
+                             terms=terms, extra=extra, term_rows=term_rows, want_out=want_out and not fp32)
         return residual if fp32 and want_out else out
 
     def forward(self, x: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:

@@ -391,7 +391,9 @@ def test_router_and_grouped_products(experts, top, hidden, ff, dtype):
     assert torch.allclose(scores.cpu().double(), torch.sigmoid(logits.gather(1, ids.cpu().long())), atol=1e-5)
     gate_up = torch.stack([torch.cat([w[f"r.e{e}.gate"], w[f"r.e{e}.up"]]) for e in range(experts)]).to(DEV)
     down = torch.stack([w[f"r.e{e}.down"] for e in range(experts)]).to(DEV)
-    y = ops.moe_experts(x.to(DEV), ids, scores, gate_up, down).cpu().double()
+    y, term_rows = ops.moe_experts(x.to(DEV), ids, scores, gate_up, down)
+    assert term_rows is None
+    y = y.cpu().double()
     wd = {k: v.double() for k, v in w.items()}
     worst = 0.0
     for t in range(n):
@@ -463,6 +465,49 @@ def test_head_norms_rotations_and_page_write(n_q, n_kv, d, real, vdim, rot_dims,
     for t in range(n):
         assert torch.allclose(again[t], outs[t, :, :vdim].double(), atol=3e-5 + 2e-6 * int(positions[t])), t
     assert torch.equal(back[..., vdim:], outs[..., vdim:])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("experts, top, hidden, ff, n", [(4, 2, 128, 128, 600), (6, 3, 64, 192, 400), (3, 1, 256, 64, 1100)])
+def test_grouped_products_on_tcgen05(experts, top, hidden, ff, n):
+    """Many (token, choice) pairs in bfloat16 with runs of 64 gate and up rows: the grouped two-SM kernel, whose
+    outputs stay in sorted order; the norm's kernel and the combining kernel pick them up through the index."""
+    from slipstream_b200 import ops
+    g = torch.Generator().manual_seed(experts + top + n)
+    x = torch.randn(n, hidden, generator=g).bfloat16()
+    w = {"r.router": (torch.randn(experts, hidden, generator=g) * 0.2).bfloat16()}
+    for e in range(experts):
+        w[f"r.e{e}.gate"] = (torch.randn(ff, hidden, generator=g) * hidden ** -0.5).bfloat16()
+        w[f"r.e{e}.up"] = (torch.randn(ff, hidden, generator=g) * hidden ** -0.5).bfloat16()
+        w[f"r.e{e}.down"] = (torch.randn(hidden, ff, generator=g) * ff ** -0.5).bfloat16()
+    ids, scores = ops.router(x.to(DEV), w["r.router"].to(DEV), top)
+
+    def runs(e):  # 64 gate rows, the 64 matching up rows, and so on
+        gate, up = w[f"r.e{e}.gate"].reshape(ff // 64, 64, hidden), w[f"r.e{e}.up"].reshape(ff // 64, 64, hidden)
+        return torch.stack([gate, up], dim=1).reshape(2 * ff, hidden)
+
+    gate_up = torch.stack([runs(e) for e in range(experts)]).to(DEV)
+    down = torch.stack([w[f"r.e{e}.down"] for e in range(experts)]).to(DEV)
+    y_sorted, place = ops.moe_experts(x.to(DEV), ids, scores, gate_up, down, run=64)
+    ops.check_errors(DEV)
+    assert place is not None and y_sorted.dtype == torch.bfloat16 and sorted(place.cpu().tolist()) == list(range(n * top))
+    y = y_sorted.cpu().double()[place.cpu().long()].reshape(n, top, hidden)
+    wd = {k: v.double() for k, v in w.items()}
+    worst = 0.0
+    for t in range(0, n, 7):
+        for k in range(top):
+            e, s = int(ids[t, k]), float(scores[t, k])
+            want = plain.gated_unit((s * x[t].double())[None], wd, f"r.e{e}")[0]
+            worst = max(worst, float((y[t, k] - want).abs().max() / want.abs().max().clamp_min(1e-3)))
+    assert worst < 4e-2
+    shared = torch.randn(n, hidden, generator=g).bfloat16()
+    combined = ops.moe_combine(y_sorted, shared.to(DEV), torch.bfloat16, place, top).cpu().double()
+    assert torch.allclose(combined, (y.sum(1) + shared.double()).bfloat16().double(), atol=1e-6)
+    stream, weight = torch.randn(n, hidden, generator=g), torch.randn(hidden, generator=g)
+    dev = stream.to(DEV)
+    ops.group_norm(y_sorted, weight.to(DEV), 2, 1e-5, torch.bfloat16, residual=dev, terms=top, extra=shared.to(DEV), term_rows=place)
+    want = stream.double() + plain.grouped_rms_norm(y.sum(1) + shared.double(), weight.double(), 2, 1e-5)
+    assert torch.allclose(dev.cpu().double(), want, atol=3e-5, rtol=1e-5)
 
 
 @pytest.mark.gpu
