@@ -751,7 +751,7 @@ def run_compare_sarudra(args) -> int:
         gate_up = [rand(experts, 2 * e_ff, h, std=0.02) for _ in range(2)]
         down = [rand(experts, h, e_ff, std=0.02) for _ in range(2)]
         before = ops.launch_count()
-        us = sweep(lambda i: ops.moe_experts(xs[i], ids, scores, gate_up[i % 2], down[i % 2]), copies=4)
+        us = sweep(lambda i: ops.moe_experts(xs[i], ids, scores, gate_up[i % 2], down[i % 2], run=64), copies=4)
         touched = len(set(ids.flatten().tolist()))
         if tag == "prefill":
             tensor("prefill_routed_experts (plan, gather, up, down)", us, 6.0 * tokens * top * h * e_ff)

@@ -23,6 +23,9 @@ __device__ __forceinline__ int request_of_row(const int32_t* __restrict__ q_star
 
 __device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-z)); }
 
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 // ---------------------------------------------------------------- grouped RMS norm
 //
 // x_i = sum_{k < terms} in[row][k * hidden + i]  (+ extra[row][i])  (* silu(gate[row][i]))
@@ -129,7 +132,9 @@ extern "C" int ss_round_stream(const float* in, void* out, int64_t n, cudaStream
 // zeros a fresh state holds.  `fused_update`: every request brings one token and the thread that read the state
 // also shifts it; otherwise conv_state_kernel does that in a launch of its own, behind this one.
 #define CONV_MAX_TAPS 8
-#define CONV_ROWS 8
+#define CONV_ROWS 32
+// A thread takes one channel over CONV_ROWS consecutive rows and keeps the channel's last T - 1 inputs in
+// registers, so every input is read once (and the few in front of the tile once more).
 template <typename T>
 __global__ void __launch_bounds__(128)
 conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const float* __restrict__ taps,
@@ -140,38 +145,53 @@ conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const flo
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    float w[CONV_MAX_TAPS];
+    float w[CONV_MAX_TAPS], x[CONV_MAX_TAPS];  // x[j]: the input T - 1 - j tokens back; x[T - 1]: the current one
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < n_taps ? taps[(int64_t)c * n_taps + j] : 0.f;
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        w[j] = j < n_taps ? taps[(int64_t)c * n_taps + j] : 0.f;
+        x[j] = 0.f;
+    }
     const float b = bias ? bias[c] : 0.f;
     const int back = n_taps - 1;
-    for (int row = blockIdx.x * CONV_ROWS; row < min(n_rows, (blockIdx.x + 1) * CONV_ROWS); ++row) {
-        const int r = request_of_row(q_start, R, row);
-        if (r < 0) break;
-        if (seq_lens[r] <= 0) continue;
-        const int slot = slots[r];
-        if (slot < 0 || slot >= n_slots) {
-            if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
-            continue;
+    const int row_end = min(n_rows, (blockIdx.x + 1) * CONV_ROWS);
+    int r = -1, r_end = -1;  // the request of the rows in front of r_end
+    bool on = false;
+    float* st = state;
+    for (int row = blockIdx.x * CONV_ROWS; row < row_end; ++row) {
+        bool fresh = row == blockIdx.x * CONV_ROWS;
+        if (row >= r_end) {
+            r = request_of_row(q_start, R, row);
+            if (r < 0) break;
+            r_end = q_start[r + 1];
+            const int slot = slots[r];
+            on = seq_lens[r] > 0 && slot >= 0 && slot < n_slots;
+            if (seq_lens[r] > 0 && !on && threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+            st = state + (int64_t)(on ? slot : 0) * back * C + c;
+            fresh = true;
         }
-        const int i = row - q_start[r];
-        float* st = state + (int64_t)slot * back * C + c;
-        float acc = b;
-        float x[CONV_MAX_TAPS];
+        if (!on) continue;
+        if (fresh) {  // the window in front of this row: earlier rows of the step, or the request's state
+            const int i = row - q_start[r];
 #pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
-            if (j >= n_taps) break;
-            const int src = i - (back - j);
-            x[j] = src >= 0 ? to_float(proj[(int64_t)(row - (back - j)) * stride + col0 + c]) : st[(int64_t)(back + src) * C];
-            acc = fmaf(w[j], x[j], acc);
+            for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+                if (j >= back) break;
+                const int src = i - (back - j);
+                x[j] = src >= 0 ? to_float(proj[(int64_t)(row - (back - j)) * stride + col0 + c]) : st[(int64_t)(back + src) * C];
+            }
         }
+        const float cur = to_float(proj[(int64_t)row * stride + col0 + c]);
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)  // (no register array is indexed by a run-time value)
+            if (j <= back) acc = fmaf(w[j], j < back ? x[j] : cur, acc);
         out[(int64_t)row * C + c] = from_float<T>(silu_exact(acc));
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+            if (j < back) x[j] = j + 1 < back ? x[j + 1] : cur;
         if (fused_update) {
 #pragma unroll
-            for (int j = 1; j < CONV_MAX_TAPS; ++j) {
-                if (j >= n_taps) break;
-                st[(int64_t)(j - 1) * C] = x[j];
-            }
+            for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+                if (j < back) st[(int64_t)j * C] = x[j];
         }
     }
 }
@@ -227,23 +247,27 @@ extern "C" int ss_conv_silu(const void* proj, int64_t stride, int col0, const fl
 // output: x at column 0, B at heads * P, C behind B), raw step dt_t (a column of the input projection):
 //   dt = softplus(dt_t + dt_bias[h]);  S <- exp(-exp(A_log[h]) dt) S + dt B_t x_t^T;  y_t = S^T C_t + D[h] x_t.
 // S is float32 [N x P] per (slot, head), stored [slot][head][P][N], carried across steps.  A block per (request,
-// head, tile of SCAN_PT columns p); NS = 8 neighbouring lanes share a column, each holding every 8th n in
-// registers; tokens run one after the other, staged SCAN_TB at a time through shared memory.  The order of the
-// arithmetic behind an output does not depend on how the request was cut into steps.
-#define SCAN_NS 8
-#define SCAN_TB 16
+// head, tile of PT <= 32 columns p); 4 neighbouring lanes share a column, each holding PER consecutive n in registers
+// (N <= 4 PER: many independent chains a thread, few shuffles a token); tokens run one after the other, staged SCAN_TB at a time through shared memory, where a
+// lane's PER values of B and of C stand together (and 4 floats apart from the next lane's, so that the 16-byte
+// loads of the 8 lanes fall on different banks).  The order of the arithmetic behind an output does not depend on
+// how the request was cut into steps.
+#define SCAN_NS 4
+#define SCAN_PT 32
 template <typename T, int PER>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(SCAN_PT * SCAN_NS)
 ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int64_t dt_stride,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, float* __restrict__ y, const int32_t* __restrict__ q_start,
                 const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ slots, int heads, int groups, int P,
                 int N, int PT, int n_slots, int* err) {
     pdl_wait();
-    extern __shared__ float sm[];
-    float* Bs = sm;                      // [TB][N]
-    float* Cs = Bs + SCAN_TB * N;        // [TB][N]
-    float* xs = Cs + SCAN_TB * N;        // [TB][PT]
+    constexpr int SCAN_TB = PER >= 64 ? 16 : 32;  // tokens staged at a time (the widest state: fewer, to stay in 48 KB)
+    constexpr int SEG = PER + 4, ROW = SCAN_NS * SEG;  // a lane's segment, a token's row of B (or C)
+    extern __shared__ __align__(16) float sm[];
+    float* Bs = sm;                      // [TB][ROW]
+    float* Cs = Bs + SCAN_TB * ROW;      // [TB][ROW]
+    float* xs = Cs + SCAN_TB * ROW;      // [TB][PT]
     float* dts = xs + SCAN_TB * PT;      // [TB]
     float* decs = dts + SCAN_TB;         // [TB]
     const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PT;
@@ -255,27 +279,56 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
         return;
     }
     const int tid = threadIdx.x, pl = tid / SCAN_NS, ns = tid % SCAN_NS;
-    const int p = p0 + pl;
-    const bool valid = pl < PT && p < P;
+    const int p = p0 + pl, n0 = ns * PER;
+    const bool valid = p < P;
     const int g = h / (heads / groups);
     const int inner = heads * P;
     float* st = state + (((int64_t)slot * heads + h) * P + (valid ? p : 0)) * N;
     float S[PER];
+    const bool vec = (N & 3) == 0;  // then a lane's values are whole 16-byte pieces
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int n = ns + SCAN_NS * i;
-        S[i] = (valid && n < N) ? st[n] : 0.f;
+    for (int i = 0; i < PER; i += 4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid && vec && n0 + i < N) v = *reinterpret_cast<const float4*>(st + n0 + i);
+        if (valid && !vec) {
+            if (n0 + i < N) v.x = st[n0 + i];
+            if (n0 + i + 1 < N) v.y = st[n0 + i + 1];
+            if (n0 + i + 2 < N) v.z = st[n0 + i + 2];
+            if (n0 + i + 3 < N) v.w = st[n0 + i + 3];
+        }
+        S[i] = v.x; S[i + 1] = v.y; S[i + 2] = v.z; S[i + 3] = v.w;
     }
     const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+    // bfloat16 rows whose B and C parts start on 16-byte boundaries are staged 8 values a load
+    const bool vec8 = sizeof(T) == 2 && (C & 7) == 0 && (inner & 7) == 0 && (N & 7) == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
+    if (vec8)  // the places behind N are never written by that path: zeros, which leave their S at zero
+        for (int i = tid; i < 2 * SCAN_TB * ROW; i += blockDim.x) Bs[i] = 0.f;
     for (int t0 = 0; t0 < q_len; t0 += SCAN_TB) {
         const int nt = min(SCAN_TB, q_len - t0);
         __syncthreads();
-        for (int idx = tid; idx < nt * N; idx += blockDim.x) {
-            const int tt = idx / N, n = idx - tt * N;
-            const T* row = xbc + (int64_t)(q0 + t0 + tt) * C;
-            Bs[tt * N + n] = to_float(row[inner + g * N + n]);
-            Cs[tt * N + n] = to_float(row[inner + groups * N + g * N + n]);
+        if (vec8) {  // 16 bytes (8 values of B or of C) a load, all of a thread's loads in flight together
+            const int chunks = N >> 3;
+#pragma unroll 4
+            for (int idx = tid; idx < nt * 2 * chunks; idx += blockDim.x) {
+                const int tt = idx / (2 * chunks), rem = idx - tt * 2 * chunks;
+                const int which = rem >= chunks, n = (rem - which * chunks) << 3;
+                const uint4 raw = *reinterpret_cast<const uint4*>(xbc + (int64_t)(q0 + t0 + tt) * C + inner + which * groups * N + g * N + n);
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                float* dst = (which ? Cs : Bs) + tt * ROW + (n / PER) * SEG + n % PER;  // PER is a multiple of 8
+                reinterpret_cast<float4*>(dst)[0] = make_float4(__low2float(h2[0]), __high2float(h2[0]), __low2float(h2[1]), __high2float(h2[1]));
+                reinterpret_cast<float4*>(dst)[1] = make_float4(__low2float(h2[2]), __high2float(h2[2]), __low2float(h2[3]), __high2float(h2[3]));
+            }
+        } else {
+#pragma unroll 4
+            for (int idx = tid; idx < nt * SCAN_NS * PER; idx += blockDim.x) {
+                const int tt = idx / (SCAN_NS * PER), n = idx - tt * (SCAN_NS * PER);
+                const T* row = xbc + (int64_t)(q0 + t0 + tt) * C + inner + g * N;
+                const int at = tt * ROW + (n / PER) * SEG + n % PER;
+                Bs[at] = n < N ? to_float(row[n]) : 0.f;  // n beyond N: zeros, which leave their S at zero
+                Cs[at] = n < N ? to_float(row[groups * N + n]) : 0.f;
+            }
         }
+#pragma unroll 4
         for (int idx = tid; idx < nt * PT; idx += blockDim.x) {
             const int tt = idx / PT, j = idx - tt * PT;
             xs[idx] = (p0 + j < P) ? to_float(xbc[(int64_t)(q0 + t0 + tt) * C + h * P + p0 + j]) : 0.f;
@@ -287,30 +340,164 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
             decs[tid] = expf(-rate * dt);
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float dec = decs[tt], xv = pl < PT ? xs[tt * PT + pl] : 0.f;
+        float* yp = y + (int64_t)(q0 + t0) * inner + h * P + p;
+#pragma unroll 4
+        for (int tt = 0; tt < nt; ++tt, yp += inner) {
+            const float dec = decs[tt], xv = xs[tt * PT + pl];
             const float dx = dts[tt] * xv;
-            float acc = 0.f;
+            const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * ROW + ns * SEG);
+            const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * ROW + ns * SEG);
+            float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int n = ns + SCAN_NS * i;
-                if (n < N) {
-                    S[i] = fmaf(dec, S[i], dx * Bs[tt * N + n]);
-                    acc = fmaf(S[i], Cs[tt * N + n], acc);
-                }
+            for (int i = 0; i < PER; i += 4) {
+                const float4 b = b4[i >> 2], c = c4[i >> 2];
+                S[i] = fmaf(dec, S[i], dx * b.x);
+                S[i + 1] = fmaf(dec, S[i + 1], dx * b.y);
+                S[i + 2] = fmaf(dec, S[i + 2], dx * b.z);
+                S[i + 3] = fmaf(dec, S[i + 3], dx * b.w);
+                acc0 = fmaf(S[i], c.x, acc0);
+                acc1 = fmaf(S[i + 1], c.y, acc1);
+                acc0 = fmaf(S[i + 2], c.z, acc0);
+                acc1 = fmaf(S[i + 3], c.w, acc1);
             }
+            float acc = acc0 + acc1;
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (ns == 0 && valid) y[(int64_t)(q0 + t0 + tt) * inner + h * P + p] = fmaf(skip, xv, acc);
+            if (ns == 0 && valid) *yp = fmaf(skip, xv, acc);
         }
     }
     if (valid) {
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int n = ns + SCAN_NS * i;
-            if (n < N) st[n] = S[i];
+        for (int i = 0; i < PER; i += 4) {
+            if (vec) {
+                if (n0 + i < N) *reinterpret_cast<float4*>(st + n0 + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (n0 + i + e < N) st[n0 + i + e] = S[i + e];
+            }
         }
+    }
+}
+
+// The same recurrence for bfloat16 rows whose parts start on 16-byte boundaries: the tokens' B, C and x are copied
+// to shared memory as they are (cp.async, 16 bytes a copy) one batch of tokens ahead of the arithmetic, into two
+// buffers that take turns, and widened to float32 as they are read (8 values a 16-byte load).
+__device__ __forceinline__ void cp_async_16_on(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+template <int PER>
+__global__ void __launch_bounds__(SCAN_PT * SCAN_NS)
+ssm_scan_bf16_kernel(const bf16* __restrict__ xbc, int C, const bf16* __restrict__ dt_raw, int64_t dt_stride,
+                     const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                     const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
+                     const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
+                     const int32_t* __restrict__ slots, int heads, int groups, int P, int N, int PT, int n_slots,
+                     int* err) {
+    pdl_wait();
+    constexpr int TB = PER >= 64 ? 16 : 32;
+    constexpr int SEGB = PER * 2 + 16, ROWB = SCAN_NS * SEGB;  // bytes: a lane's segment (16 apart from the next), a token's row
+    extern __shared__ __align__(16) unsigned char raw_sm[];
+    // per stage: B rows, C rows, x rows; behind both stages: the step sizes and decays of both
+    const int stage_bytes = 2 * TB * ROWB + TB * PT * 2;
+    float* dts = reinterpret_cast<float*>(raw_sm + 2 * stage_bytes);  // [2][TB]
+    float* decs = dts + 2 * TB;                                        // [2][TB]
+    const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PT;
+    const int q0 = q_start[r], q_len = q_start[r + 1] - q0;
+    if (q_len <= 0 || seq_lens[r] <= 0) return;
+    const int slot = slots[r];
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        return;
+    }
+    const int tid = threadIdx.x, pl = tid / SCAN_NS, ns = tid % SCAN_NS;
+    const int p = p0 + pl, n0 = ns * PER;
+    const bool valid = p < P;
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    float* st = state + (((int64_t)slot * heads + h) * P + (valid ? p : 0)) * N;
+    float S[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i += 4) {  // N is a multiple of 8 here
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid && n0 + i < N) v = *reinterpret_cast<const float4*>(st + n0 + i);
+        S[i] = v.x; S[i + 1] = v.y; S[i + 2] = v.z; S[i + 3] = v.w;
+    }
+    const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+    for (int i = tid * 16; i < 2 * stage_bytes; i += blockDim.x * 16)  // what no copy writes (n beyond N) stays zero
+        *reinterpret_cast<uint4*>(raw_sm + i) = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    const int chunks = N >> 3, x_chunks = PT >> 3;
+    auto issue = [&](int stage, int t0, int nt) {
+        unsigned char* base = raw_sm + stage * stage_bytes;
+        for (int idx = tid; idx < nt * 2 * chunks; idx += blockDim.x) {
+            const int tt = idx / (2 * chunks), rem = idx - tt * 2 * chunks;
+            const int which = rem >= chunks, n = (rem - which * chunks) << 3;
+            cp_async_16_on(base + which * TB * ROWB + tt * ROWB + (n / PER) * SEGB + (n % PER) * 2,
+                           xbc + (int64_t)(q0 + t0 + tt) * C + inner + which * groups * N + g * N + n);
+        }
+        for (int idx = tid; idx < nt * x_chunks; idx += blockDim.x) {
+            const int tt = idx / x_chunks, c = idx - tt * x_chunks;
+            if (p0 + 8 * c < P)
+                cp_async_16_on(base + 2 * TB * ROWB + (tt * PT + 8 * c) * 2, xbc + (int64_t)(q0 + t0 + tt) * C + h * P + p0 + 8 * c);
+        }
+    };
+    const int n_batches = (q_len + TB - 1) / TB;
+    issue(0, 0, min(TB, q_len));
+    cp_async_commit();
+    float dt_next = (tid < min(TB, q_len)) ? to_float(dt_raw[(int64_t)(q0 + tid) * dt_stride + h]) : 0.f;
+    for (int k = 0; k < n_batches; ++k) {
+        const int t0 = k * TB, nt = min(TB, q_len - t0), buf = k & 1;
+        if (tid < nt) {
+            const float z = dt_next + bias;
+            const float dt = z > 20.f ? z : log1pf(expf(z));
+            dts[buf * TB + tid] = dt;
+            decs[buf * TB + tid] = expf(-rate * dt);
+        }
+        if (k + 1 < n_batches) {
+            const int nt1 = min(TB, q_len - t0 - TB);
+            issue(buf ^ 1, t0 + TB, nt1);
+            if (tid < nt1) dt_next = to_float(dt_raw[(int64_t)(q0 + t0 + TB + tid) * dt_stride + h]);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const unsigned char* base = raw_sm + buf * stage_bytes;
+        const bf16* xs = reinterpret_cast<const bf16*>(base + 2 * TB * ROWB);
+        float* yp = y + (int64_t)(q0 + t0) * inner + h * P + p;
+#pragma unroll 2
+        for (int tt = 0; tt < nt; ++tt, yp += inner) {
+            const float dec = decs[buf * TB + tt], xv = to_float(xs[tt * PT + pl]);
+            const float dx = dts[buf * TB + tt] * xv;
+            const uint4* b8 = reinterpret_cast<const uint4*>(base + tt * ROWB + ns * SEGB);
+            const uint4* c8 = reinterpret_cast<const uint4*>(base + TB * ROWB + tt * ROWB + ns * SEGB);
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; i += 8) {
+                const uint4 bw = b8[i >> 3], cw = c8[i >> 3];
+                const uint32_t bb[4] = {bw.x, bw.y, bw.z, bw.w}, cc[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float b_lo = __uint_as_float(bb[e] << 16), b_hi = __uint_as_float(bb[e] & 0xffff0000u);
+                    const float c_lo = __uint_as_float(cc[e] << 16), c_hi = __uint_as_float(cc[e] & 0xffff0000u);
+                    S[i + 2 * e] = fmaf(dec, S[i + 2 * e], dx * b_lo);
+                    S[i + 2 * e + 1] = fmaf(dec, S[i + 2 * e + 1], dx * b_hi);
+                    acc0 = fmaf(S[i + 2 * e], c_lo, acc0);
+                    acc1 = fmaf(S[i + 2 * e + 1], c_hi, acc1);
+                }
+            }
+            float acc = acc0 + acc1;
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (ns == 0 && valid) *yp = fmaf(skip, xv, acc);
+        }
+        __syncthreads();  // the buffer is free for the copies of the batch after next
+    }
+    cp_async_wait<0>();
+    if (valid) {
+#pragma unroll
+        for (int i = 0; i < PER; i += 4)
+            if (n0 + i < N) *reinterpret_cast<float4*>(st + n0 + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
     }
 }
 
@@ -320,17 +507,33 @@ extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t d
                            int n_slots, int dtype, int* err, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (N < 1 || N > 256 || P < 1 || groups < 1 || heads % groups) return (int)cudaErrorInvalidValue;
-    const int PT = min((P + 3) / 4 * 4, 128);
+    const int PT = P >= SCAN_PT ? SCAN_PT : (P + 7) / 8 * 8;  // a block of PT * 4 threads: whole warps
     const dim3 grid(R, heads, (P + PT - 1) / PT), block(PT * SCAN_NS);
-    const int smem = (2 * SCAN_TB * N + SCAN_TB * PT + 2 * SCAN_TB) * 4;
-    const int per = (N + SCAN_NS - 1) / SCAN_NS;
+    const int per = N <= 32 ? 8 : (N <= 64 ? 16 : (N <= 128 ? 32 : 64));
+    const int tb = per >= 64 ? 16 : 32;
+    const int smem = (2 * tb * SCAN_NS * (per + 4) + tb * PT + 2 * tb) * 4;
+    if (dtype == SS_BF16 && C % 8 == 0 && (heads * P) % 8 == 0 && N % 8 == 0 && P % 8 == 0 && ((uintptr_t)xbc & 15) == 0 &&
+        ((uintptr_t)state & 15) == 0) {
+        const int stage = 2 * tb * SCAN_NS * (per * 2 + 16) + tb * PT * 2;
+        const int smem16 = 2 * stage + 4 * tb * 4;
+#define SCAN16_GO(PER)                                                                                                  \
+    ss_launch(ssm_scan_bf16_kernel<PER>, grid, block, smem16, stream, (const bf16*)xbc, C, (const bf16*)dt_raw, dt_stride,  \
+              dt_bias, a_log, d_skip, state, y, q_start, seq_lens, slots, heads, groups, P, N, PT, n_slots, err)
+        if (per == 8) SCAN16_GO(8);
+        else if (per == 16) SCAN16_GO(16);
+        else if (per == 32) SCAN16_GO(32);
+        else SCAN16_GO(64);
+#undef SCAN16_GO
+        return SS_LAUNCH_CHECK();
+    }
 #define SCAN_GO(T, PER)                                                                                                 \
     ss_launch(ssm_scan_kernel<T, PER>, grid, block, smem, stream, (const T*)xbc, C, (const T*)dt_raw, dt_stride, dt_bias,     \
               a_log, d_skip, state, y, q_start, seq_lens, slots, heads, groups, P, N, PT, n_slots, err)
 #define SCAN_PICK(T)                                                                                                    \
-    if (per <= 8) SCAN_GO(T, 8);                                                                                        \
-    else if (per <= 16) SCAN_GO(T, 16);                                                                                 \
-    else SCAN_GO(T, 32)
+    if (per == 8) SCAN_GO(T, 8);                                                                                        \
+    else if (per == 16) SCAN_GO(T, 16);                                                                                 \
+    else if (per == 32) SCAN_GO(T, 32);                                                                                 \
+    else SCAN_GO(T, 64)
     if (dtype == SS_BF16) { SCAN_PICK(bf16); }
     else { SCAN_PICK(float); }
 #undef SCAN_PICK
@@ -587,8 +790,6 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool on)
     const int bytes = on ? 16 : 0;  // 0: the 16 bytes are filled with zeros
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ void ldsm_x4(uint32_t r[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
@@ -834,57 +1035,56 @@ norm_rope_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* 
         T* dst = src;
         if (slot >= 0 && is_k) dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
         if (slot >= 0 && is_v) dst = kv + ((((page * 2 + 1) * n_kv + (h - n_q - n_kv)) * page_size + off) * (int64_t)D);
-        constexpr int EPL = 8;  // elements per lane: D <= 256
-        float x[EPL];
-        float ss = 0.f;
-#pragma unroll
-        for (int c = 0; c < EPL; ++c) {
-            const int d = lane + 32 * c;
-            x[c] = d < D ? to_float(src[d]) : 0.f;
-            if (d < norm_dim) ss = fmaf(x[c], x[c], ss);
-        }
-        if (!is_v && norm_dim > 0) {
-            const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)norm_dim + eps);
-            const float* w = is_k ? k_weight : q_weight;
-#pragma unroll
-            for (int c = 0; c < EPL; ++c) {
-                const int d = lane + 32 * c;
-                if (d < norm_dim) x[c] = x[c] * rstd * w[d];
-            }
-        }
         const int dims = is_v ? v_rot_dim : rot_dim, half = dims >> 1;
         const float* cs = is_v ? vcos_s : cos_s;
         const float* sn = is_v ? vsin_s : sin_s;
-        // the partner of element d lives in another lane (or another register of this lane): through shared-free
-        // shuffles only when the distance is a multiple of 32, so go through the rounded values in registers
-        float partner[EPL];
+        const bool normed = !is_v && norm_dim > 0;
+        const float* w = is_k ? k_weight : q_weight;
+        // a lane holds up to 4 rotated pairs (u, v) and up to 8 elements behind the rotated part
+        constexpr int PPL = 4, TPL = 8;
+        float u[PPL], v[PPL], tail[TPL];
+        float ss = 0.f;
 #pragma unroll
-        for (int c = 0; c < EPL; ++c) {
-            const int d = lane + 32 * c;
-            int pd = d;
-            if (d < dims) pd = interleaved ? (d ^ 1) : (d < half ? d + half : d - half);
-            // fetch x of element pd: register pd / 32 of lane pd % 32
-            float v = 0.f;
-#pragma unroll
-            for (int cc = 0; cc < EPL; ++cc) {
-                const float got = __shfl_sync(0xffffffffu, x[cc], pd & 31);
-                if ((pd >> 5) == cc) v = got;
+        for (int c = 0; c < PPL; ++c) {
+            const int i = lane + 32 * c;
+            u[c] = v[c] = 0.f;
+            if (i < half) {
+                const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+                u[c] = to_float(src[iu]);
+                v[c] = to_float(src[iv]);
+                if (iu < norm_dim) ss = fmaf(u[c], u[c], ss);
+                if (iv < norm_dim) ss = fmaf(v[c], v[c], ss);
             }
-            partner[c] = v;
         }
 #pragma unroll
-        for (int c = 0; c < EPL; ++c) {
-            const int d = lane + 32 * c;
-            if (d >= D) break;
-            float v = x[c];
-            if (d < dims) {
-                const bool first = interleaved ? !(d & 1) : d < half;
-                const int i = interleaved ? (d >> 1) : (first ? d : d - half);
-                // (u, v) -> (u c - v s, v c + u s)
-                v = first ? __fadd_rn(__fmul_rn(x[c], cs[i]), __fmul_rn(-partner[c], sn[i]))
-                          : __fadd_rn(__fmul_rn(x[c], cs[i]), __fmul_rn(partner[c], sn[i]));
+        for (int c = 0; c < TPL; ++c) {
+            const int d = dims + lane + 32 * c;
+            tail[c] = d < D ? to_float(src[d]) : 0.f;
+            if (d < norm_dim) ss = fmaf(tail[c], tail[c], ss);
+        }
+        float rstd = 1.f;
+        if (normed) rstd = 1.0f / sqrtf(warp_sum(ss) / (float)norm_dim + eps);
+#pragma unroll
+        for (int c = 0; c < PPL; ++c) {
+            const int i = lane + 32 * c;
+            if (i >= half) break;
+            const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+            float a = u[c], b = v[c];
+            if (normed) {
+                a = iu < norm_dim ? a * rstd * w[iu] : 0.f;
+                b = iv < norm_dim ? b * rstd * w[iv] : 0.f;
             }
-            dst[d] = from_float<T>(v);
+            // (u, v) -> (u c - v s, v c + u s)
+            dst[iu] = from_float<T>(__fadd_rn(__fmul_rn(a, cs[i]), __fmul_rn(-b, sn[i])));
+            dst[iv] = from_float<T>(__fadd_rn(__fmul_rn(b, cs[i]), __fmul_rn(a, sn[i])));
+        }
+#pragma unroll
+        for (int c = 0; c < TPL; ++c) {
+            const int d = dims + lane + 32 * c;
+            if (d >= D) break;
+            float a = tail[c];
+            if (normed) a = d < norm_dim ? a * rstd * w[d] : 0.f;
+            dst[d] = from_float<T>(a);
         }
     }
 }
