@@ -41,7 +41,8 @@ __device__ __forceinline__ float term_at(const TI* __restrict__ in, const TI* __
     return to_float(src[(int64_t)k * hidden + i]);
 }
 
-template <typename TI, typename TG, typename TO>
+// PLAIN: one term, no index, nothing added, no gate (a branch's output as it is), with nothing to ask per element.
+template <typename TI, typename TG, typename TO, bool PLAIN>
 __global__ void __launch_bounds__(256)
 group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const TO* __restrict__ extra,
                   const TG* __restrict__ gate, int64_t gate_stride, const float* __restrict__ weight,
@@ -55,17 +56,22 @@ group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const
     const int gw = groups >= 8 ? 1 : 8 / groups;  // warps that share a group
     const int at_once = 8 / gw;                   // groups the block holds at a time
     const TI* src = in + row * in_stride;
+    auto value_at = [&](int i) -> float {
+        if (PLAIN) return to_float(src[i]);
+        float x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
+        for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
+        if (extra) x += to_float(extra[row * hidden + i]);
+        if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
+        return x;
+    };
     for (int g0 = 0; g0 < groups; g0 += at_once) {
         const int g = g0 + warp / gw, wi = warp % gw;
         const bool on = g < groups && warp < at_once * gw;
         float ss = 0.f;
         if (on) {
+#pragma unroll 4
             for (int j = wi * 32 + lane; j < gs; j += gw * 32) {
-                const int i = g * gs + j;
-                float x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
-                for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
-                if (extra) x += to_float(extra[row * hidden + i]);
-                if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
+                const float x = value_at(g * gs + j);
                 ss = fmaf(x, x, ss);
             }
             ss = warp_sum(ss);
@@ -77,13 +83,10 @@ group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const
             float total = 0.f;
             for (int k = 0; k < gw; ++k) total += part[(warp / gw) * gw + k];
             const float rstd = 1.0f / sqrtf(total / (float)gs + eps);
+#pragma unroll 4
             for (int j = wi * 32 + lane; j < gs; j += gw * 32) {
                 const int i = g * gs + j;
-                float x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
-                for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
-                if (extra) x += to_float(extra[row * hidden + i]);
-                if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
-                float y = x * rstd * weight[i];
+                float y = value_at(i) * rstd * weight[i];
                 if (residual) {
                     y += residual[row * hidden + i];
                     residual[row * hidden + i] = y;
@@ -101,12 +104,17 @@ extern "C" int ss_group_norm(const void* in, int in_f32, int64_t in_stride, int 
                              const int32_t* term_rows) {
     if (n_out <= 0) return 0;
     if (groups < 1 || hidden % groups || terms < 1) return (int)cudaErrorInvalidValue;
+    const bool plain = terms == 1 && !term_rows && !extra && !gate;
 #define GN_GO(TI, T)                                                                                                  \
-    ss_launch(group_norm_kernel<TI, T, T>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms,        \
-              (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows)
-    if (dtype == SS_F32) GN_GO(float, float);
-    else if (in_f32) GN_GO(float, bf16);
-    else GN_GO(bf16, bf16);
+    if (plain)                                                                                                        \
+        ss_launch(group_norm_kernel<TI, T, T, true>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms,  \
+                  (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows); \
+    else                                                                                                              \
+        ss_launch(group_norm_kernel<TI, T, T, false>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms, \
+                  (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows)
+    if (dtype == SS_F32) { GN_GO(float, float); }
+    else if (in_f32) { GN_GO(float, bf16); }
+    else { GN_GO(bf16, bf16); }
 #undef GN_GO
     return SS_LAUNCH_CHECK();
 }
@@ -157,7 +165,8 @@ conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const flo
     int r = -1, r_end = -1;  // the request of the rows in front of r_end
     bool on = false;
     float* st = state;
-    for (int row = blockIdx.x * CONV_ROWS; row < row_end; ++row) {
+    const int row_first = blockIdx.x * CONV_ROWS;
+    for (int row = row_first; row < row_end; ++row) {
         bool fresh = row == blockIdx.x * CONV_ROWS;
         if (row >= r_end) {
             r = request_of_row(q_start, R, row);
@@ -301,8 +310,10 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
     const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
     // bfloat16 rows whose B and C parts start on 16-byte boundaries are staged 8 values a load
     const bool vec8 = sizeof(T) == 2 && (C & 7) == 0 && (inner & 7) == 0 && (N & 7) == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
-    if (vec8)  // the places behind N are never written by that path: zeros, which leave their S at zero
-        for (int i = tid; i < 2 * SCAN_TB * ROW; i += blockDim.x) Bs[i] = 0.f;
+    if (vec8 && N < SCAN_NS * PER) {  // the places behind N are never written by that path: zeros, which leave their S at zero
+        const int used = min(SCAN_TB, q_len) * ROW;
+        for (int i = tid; i < used; i += blockDim.x) Bs[i] = Cs[i] = 0.f;
+    }
     for (int t0 = 0; t0 < q_len; t0 += SCAN_TB) {
         const int nt = min(SCAN_TB, q_len - t0);
         __syncthreads();
@@ -504,7 +515,7 @@ ssm_scan_bf16_kernel(const bf16* __restrict__ xbc, int C, const bf16* __restrict
 extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t dt_stride, const float* dt_bias,
                            const float* a_log, const float* d_skip, float* state, float* y, const int32_t* q_start,
                            const int32_t* seq_lens, const int32_t* slots, int R, int heads, int groups, int P, int N,
-                           int n_slots, int dtype, int* err, cudaStream_t stream) {
+                           int n_slots, int dtype, int* err, cudaStream_t stream, int long_rows) {
     if (R <= 0) return 0;
     if (N < 1 || N > 256 || P < 1 || groups < 1 || heads % groups) return (int)cudaErrorInvalidValue;
     const int PT = P >= SCAN_PT ? SCAN_PT : (P + 7) / 8 * 8;  // a block of PT * 4 threads: whole warps
@@ -512,7 +523,7 @@ extern "C" int ss_ssm_scan(const void* xbc, int C, const void* dt_raw, int64_t d
     const int per = N <= 32 ? 8 : (N <= 64 ? 16 : (N <= 128 ? 32 : 64));
     const int tb = per >= 64 ? 16 : 32;
     const int smem = (2 * tb * SCAN_NS * (per + 4) + tb * PT + 2 * tb) * 4;
-    if (dtype == SS_BF16 && C % 8 == 0 && (heads * P) % 8 == 0 && N % 8 == 0 && P % 8 == 0 && ((uintptr_t)xbc & 15) == 0 &&
+    if (long_rows && dtype == SS_BF16 && C % 8 == 0 && (heads * P) % 8 == 0 && N % 8 == 0 && P % 8 == 0 && ((uintptr_t)xbc & 15) == 0 &&
         ((uintptr_t)state & 15) == 0) {
         const int stage = 2 * tb * SCAN_NS * (per * 2 + 16) + tb * PT * 2;
         const int smem16 = 2 * stage + 4 * tb * 4;
@@ -822,20 +833,20 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ x, const float* __res
     *reinterpret_cast<uint4*>(sorted + (int64_t)s * K + c * 8) = make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-#define MM_BK 32
-#define MM_STR (MM_BK + 8)
-#define MM_STAGES 3
-template <int BM, bool UP>
-constexpr int moe_mma_smem() { return MM_STAGES * (BM + (UP ? 128 : 64)) * MM_STR * 2; }
+// MM_BK: columns of K a stage holds; MM_STAGES: stages of the ring.  Tiles of few rows (decode steps) stream an
+// expert's weights once and are bound by the bytes in flight: deeper and wider stages; tiles of 128 rows are bound by
+// the tensor pipe and keep more blocks on an SM with smaller ones.
+template <int BM, bool UP, int MM_BK, int MM_STAGES>
+constexpr int moe_mma_smem() { return MM_STAGES * (BM + (UP ? 128 : 64)) * (MM_BK + 8) * 2; }
 
-template <int BM, int WARPS_M, bool UP>
+template <int BM, int WARPS_M, bool UP, int MM_BK, int MM_STAGES>
 __global__ void __launch_bounds__(256)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, const int32_t* __restrict__ perm,
                     const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_row0,
                     const int32_t* __restrict__ tile_rows, bf16* __restrict__ hidden, float* __restrict__ y, int K,
                     int n_out, int run) {
     constexpr int WARPS_N = 8 / WARPS_M, TM = BM / WARPS_M, TN = 64 / WARPS_N, MT = TM / 16, NT = TN / 8;
-    constexpr int NB = UP ? 128 : 64, U = UP ? 2 : 1;
+    constexpr int NB = UP ? 128 : 64, U = UP ? 2 : 1, MM_STR = MM_BK + 8, CPR = MM_BK / 8;  // 16-byte chunks a row
     static_assert(TM % 16 == 0 && TN % 16 == 0, "a warp's tile is whole m16 x n16 pieces");
     pdl_wait();
     const int e = tile_expert[blockIdx.x];
@@ -851,13 +862,13 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, cons
     auto load_stage = [&](int stage, int k0) {
         bf16* as = As + stage * BM * MM_STR;
         bf16* bs = Bs + stage * NB * MM_STR;
-        for (int c = tid; c < BM * 4; c += 256) {
-            const int r = c >> 2, kc = (c & 3) * 8;
+        for (int c = tid; c < BM * CPR; c += 256) {
+            const int r = c / CPR, kc = (c % CPR) * 8;
             const bool on = r < rows && k0 + kc < K;
             cp_async_16(as + r * MM_STR + kc, A + (on ? (int64_t)(row0 + r) * K + k0 + kc : 0), on);
         }
-        for (int c = tid; c < NB * 4; c += 256) {
-            const int r = c >> 2, kc = (c & 3) * 8;
+        for (int c = tid; c < NB * CPR; c += 256) {
+            const int r = c / CPR, kc = (c % CPR) * 8;
             const int n = n0 + (r & 63);
             const bool on = n < n_out && k0 + kc < K;
             // UP: gate and up rows alternate in runs of `run`; rows 0..63 of the tile are gate rows, 64..127 the up rows
@@ -931,14 +942,14 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, cons
         }
 }
 
-template <int BM, int WARPS_M, bool UP>
+template <int BM, int WARPS_M, bool UP, int MM_BK, int MM_STAGES>
 static int launch_moe_mma(const void* A, const void* W, const int32_t* perm, const int32_t* tile_expert,
                           const int32_t* tile_row0, const int32_t* tile_rows, void* hidden, float* y, int K, int n_out,
                           int max_tiles, int run, cudaStream_t stream) {
-    constexpr int smem = moe_mma_smem<BM, UP>();
+    constexpr int smem = moe_mma_smem<BM, UP, MM_BK, MM_STAGES>();
     static SsPerDevice opted;
-    if (int rc = ss_opt_in_smem(moe_gemm_mma_kernel<BM, WARPS_M, UP>, smem, opted)) return rc;
-    ss_launch(moe_gemm_mma_kernel<BM, WARPS_M, UP>, dim3(max_tiles, (n_out + 63) / 64), dim3(256), smem, stream,
+    if (int rc = ss_opt_in_smem(moe_gemm_mma_kernel<BM, WARPS_M, UP, MM_BK, MM_STAGES>, smem, opted)) return rc;
+    ss_launch(moe_gemm_mma_kernel<BM, WARPS_M, UP, MM_BK, MM_STAGES>, dim3(max_tiles, (n_out + 63) / 64), dim3(256), smem, stream,
               (const bf16*)A, (const bf16*)W, perm, tile_expert, tile_row0, tile_rows, (bf16*)hidden, y, K, n_out, run);
     return SS_LAUNCH_CHECK();
 }
@@ -953,10 +964,10 @@ extern "C" int ss_moe_gemm_mma(const void* A, const void* W, const int32_t* perm
     if (K % 8 || n_out % 8 || (tile != 128 && tile != 32) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
         return (int)cudaErrorInvalidValue;
     if (tile == 128)
-        return up ? launch_moe_mma<128, 4, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
-                  : launch_moe_mma<128, 4, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
-    return up ? launch_moe_mma<32, 2, true>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
-              : launch_moe_mma<32, 2, false>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
+        return up ? launch_moe_mma<128, 4, true, 32, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
+                  : launch_moe_mma<128, 4, false, 32, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
+    return up ? launch_moe_mma<32, 2, true, 64, 4>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
+              : launch_moe_mma<32, 2, false, 64, 4>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
 }
 
 extern "C" int ss_moe_gather(const void* x, const float* weights, const int32_t* perm, void* sorted, int total, int top,

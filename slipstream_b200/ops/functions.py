@@ -65,7 +65,7 @@ _OPS_SIGNATURES = {
     "ss_conv_silu": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_ssm_scan": [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "ss_router": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ss_moe_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -1488,7 +1488,7 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
                                      a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), y.data_ptr(),
                                      ctx.q_start.data_ptr(), ctx.seq_lens.data_ptr(), ctx.state_slots.data_ptr(),
                                      ctx.num_requests, heads, groups, head_dim, state_dim, state.shape[0], _code(xbc.dtype),
-                                     error_word(xbc.device).data_ptr(), _stream()), "ssm_scan")
+                                     error_word(xbc.device).data_ptr(), _stream(), int(not ctx.is_decode_only)), "ssm_scan")
     return y
 
 

@@ -591,6 +591,28 @@ def test_a_window_off_by_one_or_a_lost_state_would_show(models, tmp_path):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_of_one_kind_of_layer_only(tmp_path, dtype):
+    """State-space layers alone (no pages at all: the engine runs on state slots only) and attention layers alone
+    (no state), cut into portions and decoded."""
+    only_state = {"architecture": "Sarudra", "vocab": 90, "width": 64, "norm": {"eps": 1e-6, "groups": 1}, "embedding": {"scale": 2.0},
+                  "layers": [layer(mamba(2, 16, 24, 1, 4, 1), dense(64)), layer(mamba(4, 8, 16, 2, 2, 2), None)]}
+    only_attention = {"architecture": "Sarudra", "vocab": 90, "width": 64, "norm": {"eps": 1e-6, "groups": 2}, "embedding": {"scale": 2.0},
+                      "logit_softcap": 20.0,
+                      "layers": [layer(attention(4, 2, 16, 16, 0.5, (16, 1000.0), window=9, softcap=8.0), dense(64)),
+                                 layer(attention(2, 1, 32, 32, 0.3, (8, 50.0)), None)]}
+    for k, config in enumerate((only_state, only_attention)):
+        folder = tmp_path / f"m{k}"
+        weights = write_model(folder, config, 500 + k)
+        reqs = {"a": tokens_of(90, 45, 41), "b": tokens_of(90, 30, 42)}
+        want = {r: plain.logits(config, weights, t) for r, t in reqs.items()}
+        schedule = [[("a", 20), ("b", 2)], [("a", 1), ("b", 17)], [("a", 24), ("b", 1)]] + [[("b", 1)]] * 10
+        got = replay(make_runner(str(folder), dtype, pages=8, seqs=2), reqs, schedule)
+        for r in reqs:
+            assert distance(got[r], want[r]) < BOUND[dtype], (k, r)
+
+
+@pytest.mark.gpu
 def test_greedy_generation_through_the_engine(models):
     """The package's entry point and scheduler: several requests at once, prompts in portions of 16, pages and state
     slots that come back; every generated token is the plain implementation's arg-max (or within a hair of it)."""
