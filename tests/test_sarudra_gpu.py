@@ -613,6 +613,28 @@ def test_models_of_one_kind_of_layer_only(tmp_path, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_at_sizes_the_tensor_core_paths_take(tmp_path, dtype):
+    """A wider model whose sizes are in steps of 64: in bfloat16 a portion of 600 tokens with two choices a token is
+    1,200 pairs, which the grouped tcgen05 products take; heads of 128 with a window of 200 take the tcgen05 prefill
+    attention and the TMA-fed decode kernel; the recurrence takes its cp.async form.  Then portions beside decoded
+    tokens, and the window passing over decoded tokens."""
+    config = {"architecture": "Sarudra", "vocab": 300, "width": 256, "norm": {"eps": 1e-6, "groups": 4}, "embedding": {"scale": 4.0},
+              "logit_softcap": 25.0,
+              "layers": [layer(mamba(8, 32, 64, 2, 4, 2), moe(2, 2, 64, shared=128)),
+                         layer(attention(4, 2, 128, 128, 0.08, (64, 100000.0), window=200, softcap=25.0), moe(2, 2, 128)),
+                         layer(mamba(4, 64, 128, 4, 3, 4), dense(256)),
+                         layer(attention(4, 4, 64, 64, 0.12, (64, 10000.0), window=64, softcap=40.0), None)]}
+    weights = write_model(tmp_path, config, 77)
+    reqs = {"a": tokens_of(300, 700, 51), "b": tokens_of(300, 260, 52)}
+    want = {r: plain.logits(config, weights, t) for r, t in reqs.items()}
+    schedule = [[("a", 600)], [("a", 70), ("b", 1)], [("a", 1), ("b", 250)]] + [[("a", 1), ("b", 1)]] * 9 + [[("a", 20)]]
+    got = replay(make_runner(str(tmp_path), dtype, pages=70, seqs=2), reqs, schedule)
+    for r in reqs:
+        assert distance(got[r], want[r]) < BOUND[dtype], r
+
+
+@pytest.mark.gpu
 def test_greedy_generation_through_the_engine(models):
     """The package's entry point and scheduler: several requests at once, prompts in portions of 16, pages and state
     slots that come back; every generated token is the plain implementation's arg-max (or within a hair of it)."""
