@@ -966,7 +966,7 @@ extern "C" int ss_moe_gemm_mma(const void* A, const void* W, const int32_t* perm
     if (tile == 128)
         return up ? launch_moe_mma<128, 4, true, 32, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
                   : launch_moe_mma<128, 4, false, 32, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
-    return up ? launch_moe_mma<32, 2, true, 64, 4>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
+    return up ? launch_moe_mma<32, 2, true, 64, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
               : launch_moe_mma<32, 2, false, 64, 4>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
 }
 
