@@ -20,8 +20,10 @@
 // and combine their unnormalised O, maxima and sums through distributed shared memory at the end: a step with
 // few query tiles behind a long prefix would otherwise last as long as its longest query tile.
 // Masking is the packed-index causal rule of slipstream/models/layers/attention.py:46-51; softmax is float32
-// (:64-88).  No window here: windowed layers, other head sizes and page sizes that do not divide 64 run the
-// mma.sync kernel of attention_mma.cuh.  Every mbarrier wait is bounded (see gemm_tc5.cu).
+// (:64-88).  Besides the causal rule a row sees what `span` says (a sliding window, a chunk, or everything: the
+// tiles begin at the first one the query tile's first row can see, and each row masks the keys in front of its own
+// lowest one), and a soft cap may squash the scaled scores.  Other head sizes and page sizes that do not divide 64
+// run the mma.sync kernel of attention_mma.cuh.  Every mbarrier wait is bounded (see gemm_tc5.cu).
 #pragma once
 
 #include <cuda.h>

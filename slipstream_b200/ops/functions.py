@@ -799,7 +799,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     rotated queries; ``ctx`` gives the rows of each request (``q_start``), the cached lengths after
     this step (``seq_lens``) and the lists of query tiles.  float32 runs the CUDA-core kernel;
     bfloat16 the tensor-core kernels: the split decode kernel when every request brings one token, else
-    the tcgen05 kernel (head size 64 or 128, no window) or the mma.sync tiled kernel.
+    the tcgen05 kernel (head size 64 or 128; windows, chunked masks and soft caps included) or the mma.sync tiled kernel.
 
     ``rope`` (only where ``fuses_rope``): queries and keys of ``qkv`` are not rotated yet and the newest keys
     and values not yet in their pages; the decode kernel does both.
