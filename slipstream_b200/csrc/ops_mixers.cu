@@ -958,7 +958,7 @@ static int launch_moe_mma(const void* A, const void* W, const int32_t* perm, con
 // hidden rows and the output one float32 row per assignment.
 extern "C" int ss_moe_gemm_mma(const void* A, const void* W, const int32_t* perm, const int32_t* tile_expert,
                                const int32_t* tile_row0, const int32_t* tile_rows, void* hidden, float* y, int K, int n_out,
-                               int max_tiles, int tile, int up, int run, cudaStream_t stream) {
+                               int max_tiles, int tile, int up, int run, int wide_stages, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     if (up && (run < 1 || n_out % run)) return (int)cudaErrorInvalidValue;
     if (K % 8 || n_out % 8 || (tile != 128 && tile != 32) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
@@ -966,6 +966,12 @@ extern "C" int ss_moe_gemm_mma(const void* A, const void* W, const int32_t* perm
     if (tile == 128)
         return up ? launch_moe_mma<128, 4, true, 32, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
                   : launch_moe_mma<128, 4, false, 32, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
+    // few pairs (one or two requests) touch few experts, whose few blocks want as many bytes in flight each as they can
+    // hold: 128-wide stages (2 experts: 97 against 160 us); more experts fill the SMs with blocks of 64-wide stages
+    // (6 experts: 180 against 204 us)
+    if (wide_stages)
+        return up ? launch_moe_mma<32, 2, true, 128, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
+                  : launch_moe_mma<32, 2, false, 128, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
     return up ? launch_moe_mma<32, 2, true, 64, 3>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream)
               : launch_moe_mma<32, 2, false, 64, 4>(A, W, perm, tile_expert, tile_row0, tile_rows, hidden, y, K, n_out, max_tiles, run, stream);
 }

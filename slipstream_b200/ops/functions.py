@@ -71,7 +71,7 @@ _OPS_SIGNATURES = {
     "ss_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ss_moe_gemm_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_int, c_int, c_void_p],
+                        c_int, c_int, c_int, c_int, c_void_p],
     "ss_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "ss_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "ss_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -1570,9 +1570,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, gate_u
     y = torch.empty((n, top, hidden), dtype=torch.float32, device=x.device)
     if tensor_cores:
         _check(lib.ss_moe_gemm_mma(gathered.data_ptr(), gate_up.data_ptr(), *lists, hidden_act.data_ptr(), None, hidden, ff,
-                                   max_tiles, tile, 1, run, _stream()), "moe_up")
+                                   max_tiles, tile, 1, run, int(a <= 4), _stream()), "moe_up")
         _check(lib.ss_moe_gemm_mma(hidden_act.data_ptr(), down.data_ptr(), *lists, None, y.data_ptr(), ff, hidden,
-                                   max_tiles, tile, 0, 0, _stream()), "moe_down")
+                                   max_tiles, tile, 0, 0, int(a <= 4), _stream()), "moe_down")
         return y, None
     _check(lib.ss_moe_gemm(x.data_ptr(), scores.data_ptr(), gate_up.data_ptr(), *lists, hidden_act.data_ptr(), None, top,
                            hidden, ff, max_tiles, 1, _code(x.dtype), run, _stream()), "moe_up")
