@@ -635,6 +635,31 @@ def test_long_portions_at_sizes_the_tensor_core_paths_take(tmp_path, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_token_far_back_is_remembered(tmp_path, dtype):
+    """Heads that hardly decay (A_log very low) carry the first token over hundreds of steps, and an unmasked
+    attention layer with sharp scores picks single keys far back: two prompts that differ in their first 40 tokens only
+    must differ 380 tokens later in the plain implementation, by several times the bound, and the engine must give each
+    its own logits, in portions and decoded."""
+    from safetensors.torch import save_file
+    config = {"architecture": "Sarudra", "vocab": 120, "width": 64, "norm": {"eps": 1e-6, "groups": 2}, "embedding": {"scale": 3.0},
+              "layers": [layer(mamba(4, 16, 32, 2, 4, 2), dense(64)),
+                         layer(attention(4, 2, 32, 32, 0.45, (32, 10000.0)), None)]}
+    weights = write_model(tmp_path, config, 91)
+    weights["l0.mix.A_log"] = torch.full((4,), -7.0).bfloat16()  # decay per token about 1 - 1e-3 dt
+    save_file(weights, str(tmp_path / "model.safetensors"))
+    first = tokens_of(120, 420, 61)
+    other = [(t + 17) % 120 for t in first[:40]] + first[40:]
+    want = {"a": plain.logits(config, weights, first), "b": plain.logits(config, weights, other)}
+    assert distance(want["b"][-20:].float(), want["a"][-20:]) > 3 * BOUND[dtype]  # the first tokens still matter at the end
+    reqs = {"a": first, "b": other}
+    schedule = [[("a", 300), ("b", 2)], [("a", 100), ("b", 398)]] + [[("a", 1), ("b", 1)]] * 20
+    got = replay(make_runner(str(tmp_path), dtype, pages=60, seqs=2), reqs, schedule)
+    for r in reqs:
+        assert distance(got[r], want[r]) < BOUND[dtype], r
+
+
+@pytest.mark.gpu
 def test_greedy_generation_through_the_engine(models):
     """The package's entry point and scheduler: several requests at once, prompts in portions of 16, pages and state
     slots that come back; every generated token is the plain implementation's arg-max (or within a hair of it)."""
