@@ -1106,6 +1106,95 @@ norm_rope_cache_kernel(T* __restrict__ rows, int64_t row_stride, const int32_t* 
     }
 }
 
+// The same for bfloat16 heads that are rotated whole in half-split pairs (rot_dim = D, values rotated whole or not
+// at all, the norm over the whole head or none, D a multiple of 16): LPH = D / 16 lanes share a head, each with 8
+// elements of the first half and the 8 they pair with, 16 bytes a load and a store.  A block per token.
+template <int LPH>
+__global__ void __launch_bounds__(256)
+norm_rope_cache_bf16x8_kernel(bf16* __restrict__ rows, int64_t row_stride, const int32_t* __restrict__ positions,
+                              const int32_t* __restrict__ slots, const float* __restrict__ inv_freq,
+                              const float* __restrict__ v_inv_freq, const float* __restrict__ q_weight,
+                              const float* __restrict__ k_weight, bf16* __restrict__ kv, int n_q, int n_kv, int D,
+                              int rotate_v, int normed, float eps, int page_size, int64_t pool_slots, int* err) {
+    pdl_wait();
+    __shared__ float cos_s[128], sin_s[128], vcos_s[128], vsin_s[128];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int half = D >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        sincosf(__fmul_rn(pos, inv_freq[i]), &sin_s[i], &cos_s[i]);
+        if (rotate_v) sincosf(__fmul_rn(pos, v_inv_freq[i]), &vsin_s[i], &vcos_s[i]);
+    }
+    int64_t slot = (slots && kv) ? (int64_t)slots[t] : -1;
+    if (slot >= pool_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        slot = -1;
+    }
+    const int64_t page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? (int)(slot % page_size) : 0;
+    bf16* row = rows + (int64_t)t * row_stride;
+    __syncthreads();
+    constexpr int HPW = 32 / LPH;
+    const int sub = lane / LPH, l = lane % LPH;
+    const int heads = n_q + 2 * n_kv;
+    for (int hb = warp * HPW; hb < heads; hb += n_warps * HPW) {  // the same trips for every lane of a warp (shuffles below)
+        const int h = hb + sub;
+        const bool on = h < heads;
+        const bool is_v = h >= n_q + n_kv, is_k = !is_v && h >= n_q;
+        float u[8], v[8];
+        float ss = 0.f;
+        if (on) {
+            const uint4 ru = *reinterpret_cast<const uint4*>(row + (int64_t)h * D + 8 * l);
+            const uint4 rv = *reinterpret_cast<const uint4*>(row + (int64_t)h * D + half + 8 * l);
+            const uint32_t wu[4] = {ru.x, ru.y, ru.z, ru.w}, wv[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                u[2 * e] = __uint_as_float(wu[e] << 16); u[2 * e + 1] = __uint_as_float(wu[e] & 0xffff0000u);
+                v[2 * e] = __uint_as_float(wv[e] << 16); v[2 * e + 1] = __uint_as_float(wv[e] & 0xffff0000u);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(u[e], u[e], fmaf(v[e], v[e], ss));
+        }
+        if (normed) {  // the whole warp takes part in the shuffles
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        }
+        if (!on) continue;
+        if (normed && !is_v) {
+            const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+            const float* w = is_k ? k_weight : q_weight;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                u[e] = u[e] * rstd * w[8 * l + e];
+                v[e] = v[e] * rstd * w[half + 8 * l + e];
+            }
+        }
+        if (!is_v || rotate_v) {
+            const float* cs = is_v ? vcos_s : cos_s;
+            const float* sn = is_v ? vsin_s : sin_s;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float c = cs[8 * l + e], s_ = sn[8 * l + e];
+                const float a = u[e], b = v[e];
+                u[e] = __fadd_rn(__fmul_rn(a, c), __fmul_rn(-b, s_));
+                v[e] = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s_));
+            }
+        }
+        bf16* dst = row + (int64_t)h * D;
+        if (slot >= 0 && is_k) dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+        if (slot >= 0 && is_v) dst = kv + ((((page * 2 + 1) * n_kv + (h - n_q - n_kv)) * page_size + off) * (int64_t)D);
+        uint32_t ou[4], ov[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(u[2 * e], u[2 * e + 1]), b = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            ou[e] = *reinterpret_cast<const uint32_t*>(&a);
+            ov[e] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(dst + 8 * l) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+        *reinterpret_cast<uint4*>(dst + half + 8 * l) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+    }
+}
+
 extern "C" int ss_norm_rope_cache(void* rows, int64_t row_stride, const int32_t* positions, const int32_t* slots,
                                   const float* inv_freq, const float* v_inv_freq, const float* q_weight,
                                   const float* k_weight, void* kv, int n_tokens, int n_q, int n_kv, int D, int rot_dim,
@@ -1120,6 +1209,20 @@ extern "C" int ss_norm_rope_cache(void* rows, int64_t row_stride, const int32_t*
     const int warps = heads >= 8 ? 8 : (heads >= 4 ? 4 : 2);
     const dim3 grid(n_tokens, (heads + warps - 1) / warps);
     const int64_t pool = num_pages * page_size;
+    if (dtype == SS_BF16 && !interleaved && D % 16 == 0 && rot_dim == D && (v_rot_dim == 0 || v_rot_dim == D) &&
+        (norm_dim == 0 || norm_dim == D) && row_stride % 8 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)kv & 15) == 0) {
+        const int lph = D / 16;  // 1 .. 16 lanes a head; the kernel takes powers of two
+#define NR8_GO(LPH)                                                                                                     \
+    ss_launch(norm_rope_cache_bf16x8_kernel<LPH>, dim3(n_tokens), dim3(256), 0, stream, (bf16*)rows, row_stride, positions,   \
+              slots, inv_freq, v_inv_freq, q_weight, k_weight, (bf16*)kv, n_q, n_kv, D, (int)(v_rot_dim == D),            \
+              (int)(norm_dim == D), eps, page_size, pool, err)
+        if (lph == 1) { NR8_GO(1); return SS_LAUNCH_CHECK(); }
+        if (lph == 2) { NR8_GO(2); return SS_LAUNCH_CHECK(); }
+        if (lph == 4) { NR8_GO(4); return SS_LAUNCH_CHECK(); }
+        if (lph == 8) { NR8_GO(8); return SS_LAUNCH_CHECK(); }
+        if (lph == 16) { NR8_GO(16); return SS_LAUNCH_CHECK(); }
+#undef NR8_GO
+    }
     if (dtype == SS_BF16)
         ss_launch(norm_rope_cache_kernel<bf16>, grid, dim3(warps * 32), 0, stream, (bf16*)rows, row_stride, positions, slots,
                   inv_freq, v_inv_freq, q_weight, k_weight, (bf16*)kv, n_q, n_kv, D, rot_dim, v_rot_dim, interleaved,

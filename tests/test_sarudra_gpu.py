@@ -511,6 +511,44 @@ def test_grouped_products_on_tcgen05(experts, top, hidden, ff, n):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n_q, n_kv, d, rotate_v, normed", [(3, 1, 64, True, True), (8, 2, 128, True, True), (2, 2, 16, False, True),
+                                                         (5, 1, 32, True, False), (1, 1, 256, True, True)])
+def test_head_kernel_with_sixteen_byte_accesses(n_q, n_kv, d, rotate_v, normed):
+    """bfloat16 heads rotated whole: the form of the kernel that takes 8 elements a load, against the plain steps."""
+    from slipstream_b200 import ops
+    g = torch.Generator().manual_seed(d + n_q)
+    n, page, pages, base = 7, 8, 5, 5000.0
+    heads = torch.randn(n, n_q + 2 * n_kv, d, generator=g).bfloat16()
+    rows = torch.cat([heads.reshape(n, -1), torch.randn(n, 8, generator=g).bfloat16()], dim=1)
+    positions = torch.tensor([0, 1, 7, 300, 2, 45, 1000], dtype=torch.int32)
+    slots = torch.tensor([3, 4, 39, 8, -1, 17, 0], dtype=torch.int32)
+    qw, kw = torch.randn(d, generator=g), torch.randn(d, generator=g)
+    f = (base ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).float()
+    dev_rows, dev_kv = rows.to(DEV), torch.zeros(pages, 2, n_kv, page, d, dtype=torch.bfloat16, device=DEV)
+    ops.norm_rope_cache(dev_rows, positions.to(DEV), slots.to(DEV), dev_kv, n_q, n_kv, d, inv_freq=f.to(DEV), rotary_dim=d,
+                        value_inv_freq=f.to(DEV) if rotate_v else None, value_rotary_dim=d if rotate_v else 0,
+                        q_weight=qw.to(DEV) if normed else None, k_weight=kw.to(DEV) if normed else None,
+                        norm_dim=d if normed else 0, eps=1e-6)
+    hd = heads.double()
+    q, k, v = hd[:, :n_q], hd[:, n_q: n_q + n_kv], hd[:, n_q + n_kv:]
+    if normed:
+        q, k = plain.grouped_rms_norm(q, qw.double(), 1, 1e-6), plain.grouped_rms_norm(k, kw.double(), 1, 1e-6)
+    q, k = plain.turn_halves(q, positions, d, base), plain.turn_halves(k, positions, d, base)
+    if rotate_v:
+        v = plain.turn_halves(v, positions, d, base)
+    out, cache = dev_rows.cpu(), dev_kv.cpu()
+    close = lambda a, b: torch.allclose(a.double(), b, atol=2e-2 * float(b.abs().max()), rtol=1e-2)  # noqa: E731
+    assert torch.equal(out[:, (n_q + 2 * n_kv) * d:], rows[:, (n_q + 2 * n_kv) * d:])
+    assert close(out[:, : n_q * d].view(n, n_q, d), q)
+    for t in range(n):
+        if int(slots[t]) < 0:
+            assert close(out[t, n_q * d: (n_q + n_kv) * d].view(n_kv, d), k[t])
+            continue
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        assert close(cache[pg, 0, :, off], k[t]) and close(cache[pg, 1, :, off], v[t]), t
+
+
+@pytest.mark.gpu
 def test_soft_cap():
     from slipstream_b200 import ops
     x = torch.linspace(-200, 200, 1001)
