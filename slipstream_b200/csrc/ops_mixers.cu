@@ -41,8 +41,9 @@ __device__ __forceinline__ float term_at(const TI* __restrict__ in, const TI* __
     return to_float(src[(int64_t)k * hidden + i]);
 }
 
-// PLAIN: one term, no index, nothing added, no gate (a branch's output as it is), with nothing to ask per element.
-template <typename TI, typename TG, typename TO, bool PLAIN>
+// MODE 0: one term, no index, nothing added, no gate (a branch's output as it is); 1: one term under a gate; 2: the
+// general form.  Each a kernel of its own, so that the simple forms ask nothing per element.
+template <typename TI, typename TG, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const TO* __restrict__ extra,
                   const TG* __restrict__ gate, int64_t gate_stride, const float* __restrict__ weight,
@@ -56,10 +57,25 @@ group_norm_kernel(const TI* __restrict__ in, int64_t in_stride, int terms, const
     const int gw = groups >= 8 ? 1 : 8 / groups;  // warps that share a group
     const int at_once = 8 / gw;                   // groups the block holds at a time
     const TI* src = in + row * in_stride;
+    // where the terms of this row start: looked up once, not per element
+    constexpr int MAXT = MODE == 2 ? 8 : 1;
+    const TI* tp[MAXT];
+#pragma unroll
+    for (int k = 0; k < MAXT; ++k)
+        tp[k] = (MODE == 2 && k < terms) ? (term_rows ? in + (int64_t)term_rows[row * terms + k] * hidden : src + (int64_t)k * hidden) : src;
     auto value_at = [&](int i) -> float {
-        if (PLAIN) return to_float(src[i]);
-        float x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
-        for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
+        if (MODE == 0) return to_float(src[i]);
+        if (MODE == 1) return to_float(src[i]) * silu_exact(to_float(gate[row * gate_stride + i]));
+        float x;
+        if (terms <= MAXT) {
+            x = to_float(tp[0][i]);
+#pragma unroll
+            for (int k = 1; k < MAXT; ++k)
+                if (k < terms) x += to_float(tp[k][i]);
+        } else {
+            x = term_at(in, src, term_rows, row, terms, hidden, 0, i);
+            for (int k = 1; k < terms; ++k) x += term_at(in, src, term_rows, row, terms, hidden, k, i);
+        }
         if (extra) x += to_float(extra[row * hidden + i]);
         if (gate) x *= silu_exact(to_float(gate[row * gate_stride + i]));
         return x;
@@ -104,17 +120,18 @@ extern "C" int ss_group_norm(const void* in, int in_f32, int64_t in_stride, int 
                              const int32_t* term_rows) {
     if (n_out <= 0) return 0;
     if (groups < 1 || hidden % groups || terms < 1) return (int)cudaErrorInvalidValue;
-    const bool plain = terms == 1 && !term_rows && !extra && !gate;
+    const int mode = (terms == 1 && !term_rows && !extra) ? (gate ? 1 : 0) : 2;
+#define GN_LAUNCH(TI, T, MODE)                                                                                        \
+    ss_launch(group_norm_kernel<TI, T, T, MODE>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms,  \
+              (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows)
 #define GN_GO(TI, T)                                                                                                  \
-    if (plain)                                                                                                        \
-        ss_launch(group_norm_kernel<TI, T, T, true>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms,  \
-                  (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows); \
-    else                                                                                                              \
-        ss_launch(group_norm_kernel<TI, T, T, false>, dim3(n_out), dim3(256), 0, stream, (const TI*)in, in_stride, terms, \
-                  (const T*)extra, (const T*)gate, gate_stride, weight, residual, (T*)out, rows, hidden, groups, eps, term_rows)
+    if (mode == 0) GN_LAUNCH(TI, T, 0);                                                                               \
+    else if (mode == 1) GN_LAUNCH(TI, T, 1);                                                                          \
+    else GN_LAUNCH(TI, T, 2)
     if (dtype == SS_F32) { GN_GO(float, float); }
     else if (in_f32) { GN_GO(float, bf16); }
     else { GN_GO(bf16, bf16); }
+#undef GN_LAUNCH
 #undef GN_GO
     return SS_LAUNCH_CHECK();
 }
@@ -205,6 +222,103 @@ conv_silu_kernel(const T* __restrict__ proj, int64_t stride, int col0, const flo
     }
 }
 
+// The same for bfloat16 with channels in steps of 8 (and the projection's rows and the first channel on 16-byte
+// boundaries) and at most 4 taps: a thread takes 8 neighbouring channels, 16 bytes a load and a store, over
+// CONV_ROWS rows.  The window of a row that is not a request's first in this tile is already in registers.
+__global__ void __launch_bounds__(128)
+conv_silu_bf16x8_kernel(const bf16* __restrict__ proj, int64_t stride, int col0, const float* __restrict__ taps,
+                        const float* __restrict__ bias, float* __restrict__ state, bf16* __restrict__ out,
+                        const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
+                        const int32_t* __restrict__ slots, int R, int n_rows, int C, int n_taps, int n_slots,
+                        int fused_update, int* err) {
+    pdl_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) return;
+    constexpr int MAXB = 3;  // taps - 1 at most
+    const int back = n_taps - 1;
+    float w[8][MAXB + 1], x[8][MAXB], b[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        b[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+        for (int j = 0; j <= MAXB; ++j) w[e][j] = j < n_taps ? taps[(int64_t)(c + e) * n_taps + j] : 0.f;
+#pragma unroll
+        for (int j = 0; j < MAXB; ++j) x[e][j] = 0.f;
+    }
+    auto widen = [](const uint4& raw, float (&v)[8]) {
+        const uint32_t q[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { v[2 * e] = __uint_as_float(q[e] << 16); v[2 * e + 1] = __uint_as_float(q[e] & 0xffff0000u); }
+    };
+    const int row_first = blockIdx.x * CONV_ROWS, row_end = min(n_rows, row_first + CONV_ROWS);
+    int r = -1, r_end = -1;
+    bool on = false;
+    float* st = state;
+    for (int row = row_first; row < row_end; ++row) {
+        bool fresh = row == row_first;
+        if (row >= r_end) {
+            r = request_of_row(q_start, R, row);
+            if (r < 0) break;
+            r_end = q_start[r + 1];
+            const int slot = slots[r];
+            on = seq_lens[r] > 0 && slot >= 0 && slot < n_slots;
+            if (seq_lens[r] > 0 && !on && threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+            st = state + (int64_t)(on ? slot : 0) * back * C + c;
+            fresh = true;
+        }
+        if (!on) continue;
+        if (fresh) {
+            const int i = row - q_start[r];
+#pragma unroll
+            for (int j = 0; j < MAXB; ++j) {
+                if (j >= back) break;
+                const int src = i - (back - j);
+                float v[8];
+                if (src >= 0) {
+                    widen(*reinterpret_cast<const uint4*>(proj + (int64_t)(row - (back - j)) * stride + col0 + c), v);
+                } else {
+                    const float4 lo = *reinterpret_cast<const float4*>(st + (int64_t)(back + src) * C);
+                    const float4 hi = *reinterpret_cast<const float4*>(st + (int64_t)(back + src) * C + 4);
+                    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e][j] = v[e];
+            }
+        }
+        float cur[8];
+        widen(*reinterpret_cast<const uint4*>(proj + (int64_t)row * stride + col0 + c), cur);
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+            float o2[2];
+#pragma unroll
+            for (int d = 0; d < 2; ++d) {
+                float acc = b[e + d];
+#pragma unroll
+                for (int j = 0; j <= MAXB; ++j)
+                    if (j <= back) acc = fmaf(w[e + d][j], j < back ? x[e + d][j < MAXB ? j : 0] : cur[e + d], acc);
+                o2[d] = silu_exact(acc);
+            }
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(o2[0], o2[1]);
+            packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        *reinterpret_cast<uint4*>(out + (int64_t)row * C + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+#pragma unroll
+            for (int j = 0; j < MAXB; ++j)
+                if (j < back) x[e][j] = (j + 1 < back) ? x[e][j + 1 < MAXB ? j + 1 : 0] : cur[e];
+        if (fused_update) {
+#pragma unroll
+            for (int j = 0; j < MAXB; ++j)
+                if (j < back) {
+                    *reinterpret_cast<float4*>(st + (int64_t)j * C) = make_float4(x[0][j], x[1][j], x[2][j], x[3][j]);
+                    *reinterpret_cast<float4*>(st + (int64_t)j * C + 4) = make_float4(x[4][j], x[5][j], x[6][j], x[7][j]);
+                }
+        }
+    }
+}
+
 // The state after the step: the last T - 1 inputs of each request, old ones kept where the step brought fewer.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -232,7 +346,12 @@ extern "C" int ss_conv_silu(const void* proj, int64_t stride, int col0, const fl
     if (n_rows <= 0 || R <= 0) return 0;
     if (n_taps < 1 || n_taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
     const dim3 grid((n_rows + CONV_ROWS - 1) / CONV_ROWS, (C + 127) / 128);
-    if (dtype == SS_BF16)
+    if (dtype == SS_BF16 && !fused_update && n_taps <= 4 && C % 8 == 0 && col0 % 8 == 0 && stride % 8 == 0 && ((uintptr_t)proj & 15) == 0 &&
+        ((uintptr_t)out & 15) == 0 && ((uintptr_t)state & 15) == 0) {
+        const dim3 grid8((n_rows + CONV_ROWS - 1) / CONV_ROWS, (C / 8 + 127) / 128);
+        ss_launch(conv_silu_bf16x8_kernel, grid8, dim3(128), 0, stream, (const bf16*)proj, stride, col0, taps, bias, state,
+                  (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
+    } else if (dtype == SS_BF16)
         ss_launch(conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)proj, stride, col0, taps, bias, state,
                   (bf16*)out, q_start, seq_lens, slots, R, n_rows, C, n_taps, n_slots, fused_update, err);
     else

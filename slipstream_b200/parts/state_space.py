@@ -65,7 +65,11 @@ class StateSpaceMixer(Mixer):
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
         n = self.names
-        self.in_weight = weights[n["in"]]
+        # rows of zeros behind the projection bring its width to a multiple of 8, so that every token's row starts on a
+        # 16-byte boundary (the kernels behind it then take 16 bytes a load); nobody reads the columns they make
+        w_in = weights[n["in"]]
+        pad = -w_in.shape[0] % 8
+        self.in_weight = torch.cat([w_in, w_in.new_zeros((pad, w_in.shape[1]))]).contiguous() if pad else w_in
         self.out_weight = weights[n["out"]]
         as_f32 = lambda t: t.to(torch.float32).contiguous()  # noqa: E731  (exact: the stored values are kept)
         self.conv_taps, self.conv_bias = as_f32(weights[n["conv"]]), as_f32(weights[n["conv_bias"]])
@@ -78,7 +82,7 @@ class StateSpaceMixer(Mixer):
     def forward(self, x: torch.Tensor, ctx, layer: LayerBinding) -> torch.Tensor:
         proj = ops.linear(x, self.in_weight)
         xbc = ops.conv_silu(proj, self.inner, self.channels, self.conv_taps, self.conv_bias, layer.state["conv"], ctx)
-        y = ops.ssm_scan(xbc, proj[:, self.inner + self.channels:], self.dt_bias, self.a_log, self.d_skip,
+        y = ops.ssm_scan(xbc, proj[:, self.inner + self.channels: self.proj_width], self.dt_bias, self.a_log, self.d_skip,
                          layer.state["ssm"], ctx, self.heads, self.groups, self.head_dim, self.state_dim)
         gated = ops.group_norm(y, self.norm_weight, self.norm_groups, self.norm_eps, self.runtime.dtype,
                                gate=proj[:, : self.inner])

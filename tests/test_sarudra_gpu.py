@@ -549,6 +549,31 @@ def test_head_kernel_with_sixteen_byte_accesses(n_q, n_kv, d, rotate_v, normed):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("taps, channels", [(4, 72), (3, 1040), (2, 16), (1, 40)])
+def test_convolution_with_sixteen_byte_accesses(taps, channels):
+    """bfloat16 rows on 16-byte boundaries: the form that takes 8 channels a thread, across steps and slots."""
+    from slipstream_b200 import ops
+    g = torch.Generator().manual_seed(taps * 10 + channels)
+    lens, slots = {"a": 70, "b": 9}, {"a": 1, "b": 2}
+    col0, width = 16, channels + 24
+    proj = {k: torch.randn(n, width, generator=g).bfloat16() for k, n in lens.items()}
+    w, b = torch.randn(channels, taps, generator=g), torch.randn(channels, generator=g)
+    want = {k: plain.silu(plain.causal_conv(v[:, col0: col0 + channels].double(), w.double(), b.double())) for k, v in proj.items()}
+    state = torch.zeros((3, taps - 1, channels), device=DEV)
+    at = {k: 0 for k in lens}
+    for step in [[("a", 35)], [("a", 1), ("b", 2)], [("a", 33), ("b", 6)], [("a", 1), ("b", 1)]]:
+        rows = torch.cat([proj[k][at[k]: at[k] + n] for k, n in step]).to(DEV)
+        ctx = step_ctx([n for _, n in step], [at[k] + n for k, n in step], [slots[k] for k, _ in step])
+        out = ops.conv_silu(rows, col0, channels, w.to(DEV), b.to(DEV), state, ctx).cpu()
+        row = 0
+        for k, n in step:
+            assert torch.allclose(out[row: row + n].double(), want[k][at[k]: at[k] + n], atol=3e-2, rtol=2e-2), (k, at[k], n)
+            row += n
+            at[k] += n
+    assert at == lens and torch.equal(state[0].cpu(), torch.zeros(taps - 1, channels))
+
+
+@pytest.mark.gpu
 def test_soft_cap():
     from slipstream_b200 import ops
     x = torch.linspace(-200, 200, 1001)
